@@ -1,0 +1,473 @@
+"""UVU graph convolution: operator object, launch wrappers, autograd chain and ``torch.library`` custom ops.
+
+Mirrors the reference's layers for this path:
+
+* ``LunaTPUVUConv`` / ``create_uvu_conv_operator`` - ``src/lunatp/interface.py:123-144,379-393``;
+* ``lunatp_uvu_conv_func`` and the ``UVUConvForward/Backward/DoubleBackward`` autograd functions -
+  ``src/lunatp/uvu_conv/interface.py:143-434``;
+* custom ops ``lunatp::uvu_conv_{forward,backward,double_backward}`` with the reference's schemas, fake
+  (shape) implementations and ``register_autograd`` chain - ``src/lunatp/uvu_conv/interface.py:18-140``.
+
+All arithmetic happens in the C-ABI library; missing cotangents are passed as null pointers and never
+materialised.  Third-order derivatives, the per-edge envelope ``env`` and ``return_l0_feat`` are not provided.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import json
+from collections.abc import Mapping
+from functools import lru_cache
+
+import numpy as np
+import torch
+
+from . import _native
+from .graph import LunaTPGraph
+from .paths import TensorProductPaths, build_uvu_conv_metadata
+
+_DTYPE_NAMES = {torch.float32: "float32", torch.float64: "float64"}
+
+
+def is_compiling() -> bool:
+    """True while Dynamo or make_fx records a graph (``src/utils/__init__.py:8-12``)."""
+    from torch.fx.experimental.proxy_tensor import get_proxy_mode
+    from torch.utils._python_dispatch import is_in_torch_dispatch_mode
+
+    return torch.compiler.is_compiling() or (is_in_torch_dispatch_mode() and get_proxy_mode() is not None)
+
+
+class _Plan:
+    """Owns a native plan handle and the host arrays it was created from."""
+
+    def __init__(self, meta: Mapping, dtype: torch.dtype):
+        lib = _native.library()
+        specs = meta["generated_specs"]
+        paths = (_native.UvuPath * len(specs))()
+        ti, tj, tk, tc = [], [], [], []
+        for record, spec in zip(paths, specs):
+            record.x_offset = int(spec["x_offset"])
+            record.y_offset = int(spec["y_offset"])
+            record.out_offset = int(spec["out_offset"])
+            record.weight_offset = int(spec["weight_offset"])
+            record.weight_stride = int(spec.get("weight_stride", 1))
+            record.channels = int(spec["channels"])
+            record.l1, record.l2, record.l3 = int(spec["l1"]), int(spec["l2"]), int(spec["l3"])
+            record.term_begin = len(ti)
+            for i, j, k, c in spec["terms"]:
+                ti.append(int(i))
+                tj.append(int(j))
+                tk.append(int(k))
+                tc.append(float(c))
+            record.term_end = len(ti)
+        self._arrays = (
+            paths,
+            np.asarray(ti, dtype=np.int32), np.asarray(tj, dtype=np.int32), np.asarray(tk, dtype=np.int32),
+            np.asarray(tc, dtype=np.float64),
+        )
+        as_ptr = lambda a, t: a.ctypes.data_as(ctypes.POINTER(t))
+        desc = _native.UvuDesc(
+            _native.dtype_code(dtype), int(meta["in1_dim"]), int(meta["in2_dim"]), int(meta["out_dim"]),
+            int(meta["weight_numel"]), len(specs), paths, len(ti),
+            as_ptr(self._arrays[1], ctypes.c_int32), as_ptr(self._arrays[2], ctypes.c_int32),
+            as_ptr(self._arrays[3], ctypes.c_int32), as_ptr(self._arrays[4], ctypes.c_double),
+        )
+        handle = ctypes.c_void_p()
+        _native.check(lib.luna_uvu_plan_create(ctypes.byref(desc), ctypes.byref(handle)))
+        self.handle = handle
+        self._destroy = lib.luna_uvu_plan_destroy
+
+    def query(self, what: int) -> int:
+        return int(_native.library().luna_uvu_plan_query(self.handle, what))
+
+    def __del__(self):
+        handle, self.handle = getattr(self, "handle", None), None
+        if handle:
+            try:
+                self._destroy(handle)
+            except Exception:  # interpreter shutdown
+                pass
+
+
+class LunaTPUVUConv:
+    """Prepared UVU convolution for one path list and dtype."""
+
+    mode = "uvu_conv"
+    index_mode = "uvu_conv"
+
+    def __init__(self, meta: Mapping, *, dtype: torch.dtype = torch.float32, index_bits: int = 32):
+        if dtype not in (torch.float32, torch.float64):
+            raise ValueError("LunaTP uvu_conv requires torch.float32 or torch.float64.")
+        if not meta["generated_specs"] or any(int(s["channels"]) <= 0 for s in meta["generated_specs"]):
+            raise ValueError("UVU convolution requires positive channels for every path")
+        self.meta = dict(meta)
+        self.compute_dtype = dtype
+        self.index_bits = index_bits
+        self.in1_dim = int(meta["in1_dim"])
+        self.in2_dim = int(meta["in2_dim"])
+        self.out_dim = int(meta["out_dim"])
+        self.weight_numel = int(meta["weight_numel"])
+        self.max_channels = int(meta.get("max_channels", max(int(s["channels"]) for s in meta["generated_specs"])))
+        self.generated_specs = list(meta["generated_specs"])
+        self.l0_dim = 0
+        self.lunatp_backend = "lunatp_uvuconv_fp64" if dtype == torch.float64 else "lunatp_uvuconv_fp32"
+        self.lunatp_dtype = dtype
+        self._plan = _Plan(self.meta, dtype)  # host-only; also validates the path list
+        self._torch_config = None
+
+    @property
+    def torch_config(self) -> str:
+        """Static description carried as a string constant through traced graphs."""
+        if self._torch_config is None:
+            meta = dict(self.meta)
+            meta["generated_specs"] = [
+                {k: ([list(t) for t in v] if k == "terms" else v) for k, v in spec.items()}
+                for spec in self.generated_specs
+            ]
+            self._torch_config = json.dumps(
+                dict(mode="uvu_conv", dtype=_DTYPE_NAMES[self.compute_dtype], index_bits=self.index_bits,
+                     out_dim=self.out_dim, l0_dim=0, weight_mode="external", meta=meta),
+                separators=(",", ":"),
+            )
+        return self._torch_config
+
+    @property
+    def uses_staged_kernels(self) -> bool:
+        return bool(self._plan.query(0))
+
+    def force_generic(self, enabled: bool = True) -> None:
+        """Route every call through the table-driven kernels (for comparisons and tests)."""
+        _native.check(_native.library().luna_uvu_plan_set_generic(self._plan.handle, int(enabled)))
+
+    def __getstate__(self):
+        return dict(meta=self.meta, dtype=self.compute_dtype, index_bits=self.index_bits)
+
+    def __setstate__(self, state):
+        self.__init__(state["meta"], dtype=state["dtype"], index_bits=state["index_bits"])
+
+    @staticmethod
+    def run(op, x, edge_attr, weight, *, graph, env=None, return_l0_feat=False):
+        return lunatp_uvu_conv_func(op, x, edge_attr, weight, graph=graph, env=env, return_l0_feat=return_l0_feat)
+
+
+def create_uvu_conv_operator(official_tp_or_meta, *, dtype=None) -> LunaTPUVUConv:
+    if dtype is None:
+        dtype = torch.float32
+    elif dtype is not torch.float32 and dtype is not torch.float64:
+        raise ValueError("LunaTP uvu_conv requires torch.float32 or torch.float64.")
+    if isinstance(official_tp_or_meta, Mapping):
+        meta = official_tp_or_meta
+        tp = None
+    else:
+        tp = TensorProductPaths.from_tensor_product(official_tp_or_meta)
+        meta = build_uvu_conv_metadata(tp, dtype)
+    op = LunaTPUVUConv(meta, dtype=dtype)
+    if tp is not None:
+        op.tp = tp
+    return op
+
+
+@lru_cache(maxsize=128)
+def compiled_config(config: str) -> dict:
+    return json.loads(config)
+
+
+@lru_cache(maxsize=128)
+def compiled_operator(config: str) -> LunaTPUVUConv:
+    settings = compiled_config(config)
+    if settings["mode"] != "uvu_conv":
+        raise NotImplementedError(f"only uvu_conv operators are provided, got {settings['mode']!r}")
+    return LunaTPUVUConv(settings["meta"], dtype=getattr(torch, settings["dtype"]), index_bits=settings["index_bits"])
+
+
+# ----------------------------------------------------------------------------------------------- launch wrappers
+
+
+def _require_cuda(tensor: torch.Tensor) -> None:
+    if not tensor.is_cuda:
+        raise RuntimeError("CUDA is required for SO3 LunaTP.")
+
+
+def _prepared(tensor: torch.Tensor | None) -> torch.Tensor | None:
+    """Contiguous and 16-byte aligned (offset views are cloned, as the reference does for vector loads,
+    ``src/lunatp/uvu_conv/kernels/backward.py:623-628``)."""
+    if tensor is None:
+        return None
+    tensor = tensor.contiguous()
+    if tensor.data_ptr() % 16:
+        tensor = tensor.clone()
+    return tensor
+
+
+def _check_inputs(op: LunaTPUVUConv, x, y, w, num_nodes, num_edges) -> None:
+    _require_cuda(x)
+    for name, t, rows, cols in (("x", x, num_nodes, op.in1_dim), ("edge_attr", y, num_edges, op.in2_dim),
+                                ("weight", w, num_edges, op.weight_numel)):
+        if t.dtype != op.compute_dtype:
+            raise TypeError(f"{name} must be {op.compute_dtype}, got {t.dtype}")
+        if t.device != x.device:
+            raise ValueError("features, weights and graph must share one CUDA device")
+        if t.ndim != 2 or t.shape[0] != rows or t.shape[1] != cols:
+            raise ValueError(f"{name} must have shape ({rows}, {cols}), got {tuple(t.shape)}")
+
+
+def _scratch(op: LunaTPUVUConv, num_nodes: int, num_edges: int, device) -> tuple[torch.Tensor | None, int]:
+    size = int(_native.library().luna_uvu_conv_scratch_bytes(op._plan.handle, num_nodes, num_edges))
+    if size <= 0:
+        return None, 0
+    return torch.empty(size, dtype=torch.uint8, device=device), size
+
+
+class _GraphView:
+    """Native graph struct built from a tensor table list (custom-op path) or a LunaTPGraph."""
+
+    def __init__(self, tables, num_nodes: int):
+        src, dst, dst_rowptr, src_rowptr, edge_ids_by_src = tables[:5]
+        self.keep = (src, dst, dst_rowptr, src_rowptr, edge_ids_by_src)
+        for t in self.keep:
+            if t.dtype != torch.int32:
+                raise OverflowError("this build supports int32 graph tables only")
+        self.num_nodes = int(num_nodes)
+        self.num_edges = int(src.numel())
+        self.struct = _native.Graph(self.num_nodes, self.num_edges, src.data_ptr(), dst.data_ptr(),
+                                    dst_rowptr.data_ptr(), src_rowptr.data_ptr(), edge_ids_by_src.data_ptr())
+
+
+def _graph_struct(graph):
+    if isinstance(graph, LunaTPGraph):
+        return graph.native(), graph.num_nodes, graph.num_edges
+    return graph.struct, graph.num_nodes, graph.num_edges
+
+
+def run_forward(op: LunaTPUVUConv, x, y, w, graph) -> torch.Tensor:
+    struct, n, e = _graph_struct(graph)
+    _check_inputs(op, x, y, w, n, e)
+    x, y, w = _prepared(x), _prepared(y), _prepared(w)
+    out = torch.empty((n, op.out_dim), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _native.check(_native.library().luna_uvu_conv_fwd(
+            op._plan.handle, ctypes.byref(struct), x.data_ptr(), y.data_ptr(), w.data_ptr(), out.data_ptr(),
+            _native.current_stream(x.device)))
+    return out
+
+
+def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True)):
+    struct, n, e = _graph_struct(graph)
+    _check_inputs(op, x, y, w, n, e)
+    x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
+    gx = torch.empty_like(x) if needs[0] else None
+    gy = torch.empty_like(y) if needs[1] else None
+    gw = torch.empty_like(w) if needs[2] else None
+    if e == 0 or n == 0:
+        return tuple(None if t is None else t.zero_() for t in (gx, gy, gw))
+    with torch.cuda.device(x.device):
+        scratch, size = _scratch(op, n, e, x.device)
+        _native.check(_native.library().luna_uvu_conv_bwd(
+            op._plan.handle, ctypes.byref(struct), x.data_ptr(), y.data_ptr(), w.data_ptr(), g.data_ptr(),
+            _native.pointer(gx), _native.pointer(gy), _native.pointer(gw), _native.pointer(scratch), size,
+            _native.current_stream(x.device)))
+    return gx, gy, gw
+
+
+def run_double_backward(op: LunaTPUVUConv, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True)):
+    struct, n, e = _graph_struct(graph)
+    _check_inputs(op, x, y, w, n, e)
+    x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
+    rx, ry, rw = _prepared(rx), _prepared(ry), _prepared(rw)
+    hx = torch.empty_like(x) if needs[0] else None
+    hy = torch.empty_like(y) if needs[1] else None
+    hw = torch.empty_like(w) if needs[2] else None
+    hg = torch.empty_like(g) if needs[3] else None
+    if e == 0 or n == 0:
+        return tuple(None if t is None else t.zero_() for t in (hx, hy, hw, hg))
+    with torch.cuda.device(x.device):
+        scratch, size = _scratch(op, n, e, x.device)
+        _native.check(_native.library().luna_uvu_conv_dbl_bwd(
+            op._plan.handle, ctypes.byref(struct), x.data_ptr(), y.data_ptr(), w.data_ptr(), g.data_ptr(),
+            _native.pointer(rx), _native.pointer(ry), _native.pointer(rw),
+            _native.pointer(hx), _native.pointer(hy), _native.pointer(hw), _native.pointer(hg),
+            _native.pointer(scratch), size, _native.current_stream(x.device)))
+    return hx, hy, hw, hg
+
+
+# ----------------------------------------------------------------------------------------------- eager autograd chain
+
+
+class UVUConvForward(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, op, x, y, w, graph):
+        ctx.op, ctx.graph = op, graph
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(x, y, w)
+        return run_forward(op, x, y, w, graph)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, y, w = ctx.saved_tensors
+        op, graph = ctx.op, ctx.graph
+        needs = ctx.needs_input_grad[1:4]
+        if grad_out is None:
+            return (None,) + tuple(torch.zeros_like(t) if need else None for t, need in zip((x, y, w), needs)) + (None,)
+        g = grad_out.contiguous()
+        if torch.is_grad_enabled():
+            gx, gy, gw = UVUConvBackward.apply(op, x, y, w, g, graph)
+        else:
+            gx, gy, gw = run_backward(op, x, y, w, g, graph, needs=needs)
+        return (None, gx if needs[0] else None, gy if needs[1] else None, gw if needs[2] else None, None)
+
+
+class UVUConvBackward(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, op, x, y, w, g, graph):
+        ctx.op, ctx.graph = op, graph
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(x, y, w, g)
+        return run_backward(op, x, y, w, g, graph, needs=(True, True, True))
+
+    @staticmethod
+    def backward(ctx, rx, ry, rw):
+        x, y, w, g = ctx.saved_tensors
+        needs = ctx.needs_input_grad[1:5]
+        if rx is None and ry is None and rw is None:
+            return (None,) * 6
+        if torch.is_grad_enabled():
+            hx, hy, hw, hg = UVUConvDoubleBackward.apply(ctx.op, x, y, w, g, rx, ry, rw, ctx.graph)
+        else:
+            hx, hy, hw, hg = run_double_backward(ctx.op, x, y, w, g, rx, ry, rw, ctx.graph, needs=needs)
+        return (None, hx if needs[0] else None, hy if needs[1] else None, hw if needs[2] else None,
+                hg if needs[3] else None, None)
+
+
+class UVUConvDoubleBackward(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, op, x, y, w, g, rx, ry, rw, graph):
+        ctx.set_materialize_grads(False)
+        return run_double_backward(op, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        if all(g is None for g in grads):
+            return (None,) * 9
+        raise NotImplementedError("third-order derivatives of the UVU convolution are not provided")
+
+
+# ----------------------------------------------------------------------------------------------- custom ops
+
+
+@torch.library.custom_op(
+    "lunatp::uvu_conv_forward", mutates_args=(),
+    schema="(Tensor x, Tensor y, Tensor w, Tensor? env, Tensor?[] tables, SymInt num_nodes, bool return_l0, "
+           "str config) -> (Tensor, Tensor?)")
+def conv_forward(x, y, w, env, tables, num_nodes, return_l0, config):
+    if env is not None or return_l0:
+        raise NotImplementedError("env and return_l0_feat are not provided")
+    op = compiled_operator(config)
+    return run_forward(op, x, y, w, _GraphView(tables, num_nodes)), None
+
+
+@conv_forward.register_fake
+def _(x, y, w, env, tables, num_nodes, return_l0, config):
+    dims = compiled_config(config)
+    return x.new_empty((num_nodes, dims["out_dim"])), None
+
+
+@torch.library.custom_op(
+    "lunatp::uvu_conv_backward", mutates_args=(),
+    schema="(Tensor x, Tensor y, Tensor w, Tensor? env, Tensor g, Tensor? gl0, Tensor?[] tables, SymInt num_nodes, "
+           "bool[] needs, str config) -> (Tensor?, Tensor?, Tensor?, Tensor?)")
+def conv_backward(x, y, w, env, g, gl0, tables, num_nodes, needs, config):
+    op = compiled_operator(config)
+    gx, gy, gw = run_backward(op, x, y, w, g, _GraphView(tables, num_nodes), needs=tuple(needs[:3]))
+    return gx, gy, gw, None
+
+
+@conv_backward.register_fake
+def _(x, y, w, env, g, gl0, tables, num_nodes, needs, config):
+    return tuple(torch.empty_like(v, memory_format=torch.contiguous_format) if need and v is not None else None
+                 for v, need in zip((x, y, w, env), needs))
+
+
+@torch.library.custom_op(
+    "lunatp::uvu_conv_double_backward", mutates_args=(),
+    schema="(Tensor x, Tensor y, Tensor w, Tensor? env, Tensor g, Tensor? gl0, Tensor? rx, Tensor? ry, Tensor? rw, "
+           "Tensor? re, Tensor?[] tables, SymInt num_nodes, bool[] needs, str config) -> "
+           "(Tensor?, Tensor?, Tensor?, Tensor?, Tensor?, Tensor?)")
+def conv_double_backward(x, y, w, env, g, gl0, rx, ry, rw, re, tables, num_nodes, needs, config):
+    op = compiled_operator(config)
+    want = (needs[0], needs[1], needs[2], needs[4])
+    hx, hy, hw, hg = run_double_backward(op, x, y, w, g, rx, ry, rw, _GraphView(tables, num_nodes), needs=want)
+    return hx, hy, hw, None, hg, None
+
+
+@conv_double_backward.register_fake
+def _(x, y, w, env, g, gl0, rx, ry, rw, re, tables, num_nodes, needs, config):
+    return tuple(torch.empty_like(v, memory_format=torch.contiguous_format) if need and v is not None else None
+                 for v, need in zip((x, y, w, env, g, gl0), needs))
+
+
+def _setup_forward(ctx, inputs, output):
+    x, y, w, env, tables, ctx.num_nodes, _, ctx.config = inputs
+    ctx.save_for_backward(x, y, w, *tables)
+    ctx.table_count = len(tables)
+    ctx.set_materialize_grads(False)
+
+
+def _forward_backward(ctx, g, gl0):
+    x, y, w, *tables = ctx.saved_tensors
+    table_grad = [None] * ctx.table_count
+    if g is None:
+        g = x.new_zeros((ctx.num_nodes, compiled_config(ctx.config)["out_dim"]))
+    needs = list(ctx.needs_input_grad[:3]) + [False]
+    gx, gy, gw, _ = conv_backward(x, y, w, None, g.contiguous(), None, tables, ctx.num_nodes, needs, ctx.config)
+    return gx, gy, gw, None, table_grad, None, None, None
+
+
+def _setup_backward(ctx, inputs, output):
+    x, y, w, env, g, gl0, tables, ctx.num_nodes, _, ctx.config = inputs
+    ctx.save_for_backward(x, y, w, g, *tables)
+    ctx.table_count = len(tables)
+    ctx.set_materialize_grads(False)
+
+
+def _backward_backward(ctx, rx, ry, rw, re):
+    x, y, w, g, *tables = ctx.saved_tensors
+    table_grad = [None] * ctx.table_count
+    if rx is None and ry is None and rw is None:
+        return None, None, None, None, None, None, table_grad, None, None, None
+    needs = [ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2], False,
+             ctx.needs_input_grad[4], False]
+    hx, hy, hw, _, hg, _ = conv_double_backward(x, y, w, None, g, None, rx, ry, rw, None, tables, ctx.num_nodes,
+                                                needs, ctx.config)
+    return hx, hy, hw, None, hg, None, table_grad, None, None, None
+
+
+conv_forward.register_autograd(_forward_backward, setup_context=_setup_forward)
+conv_backward.register_autograd(_backward_backward, setup_context=_setup_backward)
+
+
+# ----------------------------------------------------------------------------------------------- functional entry
+
+
+def lunatp_uvu_conv_func(op: LunaTPUVUConv, x, edge_attr, weight, *, graph: LunaTPGraph, env=None,
+                         return_l0_feat: bool = False):
+    """Aggregate UVU edge messages by destination, differentiable to second order.
+
+    ``x`` [num_nodes, in1_dim], ``edge_attr`` [num_edges, in2_dim], ``weight`` [num_edges, weight_numel] share one
+    CUDA device and the operator's dtype; edge data follows the order of the graph's edge list.
+    """
+    if env is not None or return_l0_feat:
+        raise NotImplementedError("env and return_l0_feat are not provided by this build")
+    if weight is None:
+        raise TypeError("UVU convolution requires explicit per-edge weights")
+    if not isinstance(graph, LunaTPGraph):
+        raise TypeError("graph must be a LunaTPGraph prepared with make_graph / create_graph")
+    if is_compiling():
+        out, _ = torch.ops.lunatp.uvu_conv_forward.default(
+            x.contiguous(), edge_attr.contiguous(), weight.contiguous(), None, graph.table_list(),
+            graph.num_nodes, False, op.torch_config)
+        return out
+    return UVUConvForward.apply(op, x, edge_attr, weight, graph)
+
+
+__all__ = ["LunaTPUVUConv", "create_uvu_conv_operator", "lunatp_uvu_conv_func", "run_forward", "run_backward",
+           "run_double_backward", "UVUConvForward", "UVUConvBackward", "UVUConvDoubleBackward"]

@@ -1,0 +1,196 @@
+// UVU convolution plan: host-side analysis of the path list and the lookup tables the kernels read.
+#pragma once
+
+#include <array>
+#include <cstdint>
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "common.h"
+
+namespace luna {
+
+// ------------------------------------------------------------------------------------------------ generic tables
+// One record per path (instruction x edge channel).  *_ptr index the three row-pointer arrays that list a path's
+// coupling terms sorted by output component k, by x component i and by y component j.
+struct PathRec {
+  int x_off, y_off, out_off, w_off, w_stride, ch;
+  int d1, d2, d3;
+  int byk_ptr, byi_ptr, byj_ptr;  // start of this path's (d+1)-entry row-pointer block in rowptr_{k,i,j}
+};
+
+// A block of a feature row shared by several paths (an irrep block of x, y or out).
+struct SlotRec {
+  int off, ch, d;          // ch = 1 for y slots
+  int path_begin, path_end;  // range in the slot's path list
+};
+
+template <typename T>
+struct TermRec {
+  int a, b;  // the two indices other than the sorting one, in (i, j, k) order
+  T c;
+};
+
+// Pointers into the per-device table buffer.
+template <typename T>
+struct GenericTables {
+  const PathRec* paths;
+  int num_paths;
+  const SlotRec *out_slots, *x_slots, *y_slots;
+  int num_out_slots, num_x_slots, num_y_slots;
+  const int *out_slot_paths, *x_slot_paths, *y_slot_paths;
+  const int* w_elem_path;  // [weight_numel] path owning each weight column, -1 if none
+  const int *rowptr_k, *rowptr_i, *rowptr_j;
+  const TermRec<T>*terms_k, *terms_i, *terms_j;
+  int X, Y, O, W;
+};
+
+// ------------------------------------------------------------------------------------------------ staged ("fast") tables
+constexpr int kMaxFastPaths = 64;
+constexpr int kMaxFastL = 3;          // degrees 0..3 on x and out
+constexpr int kMaxPieces = 80;        // bulk-copy pieces per edge stage
+constexpr int kMaxMEntries = 2048;
+
+struct CopyPiece {
+  int g_off;   // element offset inside the global row for channel chunk 0
+  int comp;    // elements per channel (multiplies the chunk's first channel)
+  int s_off;   // element offset inside the shared-memory region
+  int n;       // elements
+};
+
+// Everything the staged kernels need, small enough to travel as a kernel parameter.
+struct FastMeta {
+  int LX, LO;                 // highest degree present in x / out
+  int cpl;                    // channels per lane
+  int chunks;                 // channel chunks per feature block
+  int ch;                     // channels per block (uniform)
+  int X, Y, O, W;
+  int num_paths;
+  int x_off[kMaxFastL + 1];   // global offset of the degree-l block of x, -1 if absent
+  int o_off[kMaxFastL + 1];
+  int xs_off[kMaxFastL + 1];  // offset of that block inside the staged x region (elements)
+  int gs_off[kMaxFastL + 1];  // offset inside the staged g region
+  int pair_ptr[(kMaxFastL + 1) * (kMaxFastL + 1) + 1];  // paths sorted by (l1, l3)
+  int w_soff[kMaxFastPaths];  // offset of a path's channel chunk inside the staged w region
+  int w_goff[kMaxFastPaths];  // global weight offset of the path
+  int m_off[kMaxFastPaths];   // offset of the path's d1 x d3 matrix in the per-edge M buffer
+  int m_total;                // entries in the M buffer (padded)
+  int w_stage_elems, x_stage_elems, g_stage_elems;
+  int n_w_pieces, n_x_pieces, n_g_pieces;
+  CopyPiece pieces_w[kMaxFastPaths];
+  CopyPiece pieces_x[kMaxFastL + 1];
+  CopyPiece pieces_g[kMaxFastL + 1];
+};
+
+// Device-resident program that turns one edge's y row into the M matrices: M[m] = sum_t c[t] * y[j[t]].
+template <typename T>
+struct MProgram {
+  const int* ptr;  // [m_total + 1]
+  const int* j;    // [terms]
+  const T* c;      // [terms]
+};
+
+// ------------------------------------------------------------------------------------------------ the plan
+struct DeviceTables {
+  void* buffer = nullptr;  // one allocation holding every table
+  size_t bytes = 0;
+  int* status = nullptr;   // device status word (inside buffer)
+  // resolved pointers (type-erased; reinterpret for the plan's dtype)
+  const PathRec* paths = nullptr;
+  const SlotRec *out_slots = nullptr, *x_slots = nullptr, *y_slots = nullptr;
+  const int *out_slot_paths = nullptr, *x_slot_paths = nullptr, *y_slot_paths = nullptr;
+  const int* w_elem_path = nullptr;
+  const int *rowptr_k = nullptr, *rowptr_i = nullptr, *rowptr_j = nullptr;
+  const void *terms_k = nullptr, *terms_i = nullptr, *terms_j = nullptr;
+  const int* m_ptr = nullptr;
+  const int* m_j = nullptr;
+  const void* m_c = nullptr;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+};
+
+}  // namespace luna
+
+struct luna_uvu_plan {
+  int dtype = LUNA_F32;
+  int X = 0, Y = 0, O = 0, W = 0;
+  std::vector<luna::PathRec> paths;
+  std::vector<luna::SlotRec> out_slots, x_slots, y_slots;
+  std::vector<int> out_slot_paths, x_slot_paths, y_slot_paths;
+  std::vector<int> w_elem_path;
+  std::vector<int> rowptr_k, rowptr_i, rowptr_j;
+  // terms kept in double on the host; narrowed at upload
+  struct HostTerm {
+    int a, b;
+    double c;
+  };
+  std::vector<HostTerm> terms_k, terms_i, terms_j;
+  bool out_fully_covered = false;
+
+  bool fast_ok = false;
+  bool force_generic = false;
+  luna::FastMeta fast{};
+  std::vector<int> m_ptr, m_j;
+  std::vector<double> m_c;
+
+  std::mutex mutex;
+  std::map<int, luna::DeviceTables> device_tables;
+};
+
+namespace luna {
+
+// Returns the tables for the current device, uploading them on first use.
+int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out);
+
+template <typename T>
+GenericTables<T> generic_tables(const luna_uvu_plan* plan, const DeviceTables& dt) {
+  GenericTables<T> t;
+  t.paths = dt.paths;
+  t.num_paths = static_cast<int>(plan->paths.size());
+  t.out_slots = dt.out_slots;
+  t.x_slots = dt.x_slots;
+  t.y_slots = dt.y_slots;
+  t.num_out_slots = static_cast<int>(plan->out_slots.size());
+  t.num_x_slots = static_cast<int>(plan->x_slots.size());
+  t.num_y_slots = static_cast<int>(plan->y_slots.size());
+  t.out_slot_paths = dt.out_slot_paths;
+  t.x_slot_paths = dt.x_slot_paths;
+  t.y_slot_paths = dt.y_slot_paths;
+  t.w_elem_path = dt.w_elem_path;
+  t.rowptr_k = dt.rowptr_k;
+  t.rowptr_i = dt.rowptr_i;
+  t.rowptr_j = dt.rowptr_j;
+  t.terms_k = static_cast<const TermRec<T>*>(dt.terms_k);
+  t.terms_i = static_cast<const TermRec<T>*>(dt.terms_i);
+  t.terms_j = static_cast<const TermRec<T>*>(dt.terms_j);
+  t.X = plan->X;
+  t.Y = plan->Y;
+  t.O = plan->O;
+  t.W = plan->W;
+  return t;
+}
+
+// Which argument of the four-linear form F(x, y, w, g) is left free (differentiated).
+enum FreeSlot { kFreeG = 0, kFreeX = 1, kFreeY = 2, kFreeW = 3 };
+
+// Table-driven contraction: out (shaped like the free argument) = or += dF/d(free).  Operands are device
+// pointers of the plan's dtype; the pointer in the free position is ignored.
+int generic_contract(luna_uvu_plan* plan, const luna_graph* graph, int free_slot, const void* x, const void* y,
+                     const void* w, const void* g, void* out, bool accumulate, cudaStream_t stream);
+
+// Staged kernels (bulk-copy pipeline).  fast_available() is false in a build without them.
+bool fast_available();
+// which: 0 forward-shaped kernel, 1 backward-shaped kernel.  Dynamic shared memory per block, 0 if not eligible.
+int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which);
+int64_t fast_scratch_bytes(const luna_uvu_plan* plan, int64_t num_nodes, int64_t num_edges);
+// tangents == false: out = F_g(x, y, w).  tangents == true: out = F_g(rx, y, w) + F_g(x, ry, w) + F_g(x, y, rw)
+// with null tangents skipped (at least one must be given).
+int fast_forward(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y, const void* w,
+                 const void* rx, const void* ry, const void* rw, void* out, bool tangents, cudaStream_t stream);
+// Any subset of gx, gy, gw (null = skip); acc_* adds to the existing contents instead of overwriting.
+int fast_backward(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y, const void* w,
+                  const void* g, void* gx, bool acc_x, void* gy, bool acc_y, void* gw, bool acc_w, void* scratch,
+                  int64_t scratch_bytes, cudaStream_t stream);
+
+}  // namespace luna

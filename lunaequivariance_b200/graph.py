@@ -1,0 +1,224 @@
+"""Graph validation and the CSR / permutation tables shared by every order of the convolution.
+
+Public behaviour follows the reference's ``make_graph`` and ``LunaTPGraph`` (``src/lunatp/graph.py:17-141``) and
+``make_source_segments`` (``src/lunatp/uvu_conv/graph.py:38-99``): same field names, same validation messages,
+inputs are copied into owned int32 tensors, ``dst`` must be ascending.  On CUDA tensors the tables are built by
+the library's ``luna_graph_build`` (radix sorts and scans on the caller's stream); CPU tensors use torch ops so
+that graphs can be prepared and inspected without a GPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from operator import index
+
+import torch
+
+from . import _native
+
+SOURCE_SEGMENT_EDGES = 32
+
+
+@dataclass(frozen=True)
+class SourceSegmentTables:
+    """Source-CSR rows cut into pieces of at most 32 edges; every node keeps at least one (possibly empty) piece."""
+
+    nodes: torch.Tensor
+    begin: torch.Tensor
+    end: torch.Tensor
+    rowptr: torch.Tensor
+    order: torch.Tensor
+
+
+@dataclass(frozen=True)
+class LunaTPGraph:
+    """Prepared topology; immutable and reusable across layers and dtypes."""
+
+    src: torch.Tensor
+    dst: torch.Tensor
+    num_nodes: int
+    dst_rowptr: torch.Tensor
+    src_rowptr: torch.Tensor
+    edge_ids_by_src: torch.Tensor
+    edge_ids_by_dst: torch.Tensor
+    node_order: torch.Tensor | None = None
+    source_node_order: torch.Tensor | None = None
+    node_tiers: torch.Tensor | None = None
+    source_segments: SourceSegmentTables | None = None
+    _tables: dict = field(default_factory=dict, init=False, repr=False, compare=False)
+
+    @property
+    def num_edges(self) -> int:
+        return int(self.src.numel())
+
+    def native(self) -> "_native.Graph":
+        """The C-ABI view of this graph (cached; the tensors it points to are owned by the graph)."""
+        view = self._tables.get("native")
+        if view is None:
+            view = _native.Graph(
+                self.num_nodes, self.num_edges, self.src.data_ptr(), self.dst.data_ptr(),
+                self.dst_rowptr.data_ptr(), self.src_rowptr.data_ptr(), self.edge_ids_by_src.data_ptr(),
+            )
+            self._tables["native"] = view
+        return view
+
+    def table_list(self) -> list:
+        """The 13 tensors the reference passes to its custom ops (``src/lunatp/uvu_conv/interface.py:186-192``)."""
+        seg = self.source_segments
+        return [self.src, self.dst, self.dst_rowptr, self.src_rowptr, self.edge_ids_by_src,
+                self.source_node_order, self.node_order,
+                seg.nodes, seg.begin, seg.end, seg.rowptr, seg.order, self.node_tiers]
+
+
+def make_source_segments(src_rowptr: torch.Tensor) -> SourceSegmentTables:
+    rowptr = src_rowptr.to(torch.int64)
+    degree = rowptr[1:] - rowptr[:-1]
+    count = ((degree + (SOURCE_SEGMENT_EDGES - 1)) // SOURCE_SEGMENT_EDGES).clamp_min(1)
+    seg_rowptr = torch.zeros(degree.numel() + 1, dtype=torch.int64, device=rowptr.device)
+    torch.cumsum(count, 0, out=seg_rowptr[1:])
+    total = int(seg_rowptr[-1].item()) if degree.numel() else 0
+    nodes = torch.repeat_interleave(torch.arange(degree.numel(), device=rowptr.device), count, output_size=total)
+    local = torch.arange(total, device=rowptr.device) - seg_rowptr[:-1][nodes]
+    begin = rowptr[nodes] + SOURCE_SEGMENT_EDGES * local
+    end = torch.minimum(begin + SOURCE_SEGMENT_EDGES, rowptr[nodes + 1])
+    by_degree = torch.argsort(degree[nodes], descending=True, stable=True)
+    order = by_degree[torch.argsort((end - begin)[by_degree], descending=True, stable=True)]
+    narrow = src_rowptr.dtype
+    return SourceSegmentTables(nodes.to(torch.int32), begin.to(narrow), end.to(narrow), seg_rowptr.to(narrow),
+                               order.to(narrow))
+
+
+def _node_tiers(dst_rowptr, node_order, num_nodes, num_edges, device):
+    if num_nodes and num_edges:
+        cumulative = dst_rowptr.diff().to(torch.int64)[node_order.long()].cumsum(0)
+        thresholds = torch.arange(1, 4, device=device, dtype=torch.int64) * num_edges // 4
+        return (torch.searchsorted(cumulative, thresholds) + 1).to(torch.int32)
+    return torch.full((3,), num_nodes, device=device, dtype=torch.int32)
+
+
+def _bounds_host(src, dst):
+    low = min(int(src.min()), int(dst.min()))
+    high = max(int(src.max()), int(dst.max()))
+    unsorted = bool((dst[1:] < dst[:-1]).any()) if src.numel() > 1 else False
+    return low, high, unsorted
+
+
+def _bounds_cuda(src, dst):
+    lib = _native.library()
+    edges = src.numel()
+    scratch_bytes = lib.luna_graph_scratch_bytes(0, edges)
+    scratch = torch.empty(max(scratch_bytes, 1), dtype=torch.uint8, device=src.device)
+    low, high, unsorted = ctypes.c_int64(0), ctypes.c_int64(-1), ctypes.c_int(0)
+    bits = 64 if src.dtype == torch.int64 else 32
+    _native.check(lib.luna_graph_bounds(src.data_ptr(), dst.data_ptr(), bits, edges, ctypes.byref(low),
+                                        ctypes.byref(high), ctypes.byref(unsorted), scratch.data_ptr(),
+                                        scratch_bytes, _native.current_stream(src.device)))
+    return low.value, high.value, bool(unsorted.value)
+
+
+def make_graph(src: torch.Tensor, dst: torch.Tensor, num_nodes: int | None = None) -> LunaTPGraph:
+    """Build the topology tables from a destination-sorted edge list.
+
+    ``src`` and ``dst`` are ``[edges]`` or ``[edges, 1]`` int32/int64 tensors on one device, ``dst`` ascending and
+    all edge data in the same order.  Build once per topology and reuse across layers.
+    """
+    if src.ndim == 2 and src.shape[1] == 1:
+        src = src.squeeze(-1)
+    if dst.ndim == 2 and dst.shape[1] == 1:
+        dst = dst.squeeze(-1)
+    if src.ndim != 1 or dst.ndim != 1 or src.shape != dst.shape:
+        raise ValueError("src and dst must have equal shape [edges] or [edges, 1].")
+    if src.dtype not in (torch.int32, torch.int64) or dst.dtype not in (torch.int32, torch.int64):
+        raise TypeError("graph indices must be int32 or int64.")
+    if src.device != dst.device:
+        raise ValueError("src and dst must be on the same device.")
+    if num_nodes is not None and not isinstance(num_nodes, int):
+        num_nodes = index(num_nodes)
+    if src.dtype != dst.dtype:
+        src, dst = src.to(torch.int64), dst.to(torch.int64)
+    src, dst = src.contiguous(), dst.contiguous()
+
+    num_edges = src.numel()
+    device = src.device
+    required = 0
+    if num_edges:
+        with torch.cuda.device(device) if device.type == "cuda" else _NullContext():
+            low, high, unsorted = (_bounds_cuda if device.type == "cuda" else _bounds_host)(src, dst)
+        if low < 0:
+            raise ValueError("graph indices must be nonnegative.")
+        if unsorted:
+            raise ValueError("dst must be sorted in ascending order; src and edge data must follow the same order.")
+        required = high + 1
+    if num_nodes is None:
+        num_nodes = required
+    if num_nodes < required:
+        raise ValueError(
+            f"num_nodes={num_nodes} must be nonnegative and at least {required} for the supplied indices.")
+    if num_nodes >= (1 << 31):
+        raise OverflowError("graph node count exceeds signed int32 capacity.")
+    if max(num_edges, num_nodes + num_edges // SOURCE_SEGMENT_EDGES) >= (1 << 31) - 1024:
+        raise OverflowError("graph edge count exceeds the int32 table capacity of this build.")
+
+    if device.type == "cuda":
+        tables = _build_cuda(src, dst, num_nodes)
+    else:
+        tables = _build_host(src, dst, num_nodes)
+    src_out, dst_out, dst_rowptr, src_rowptr, edge_ids_by_src, node_order, source_node_order = tables
+    graph = LunaTPGraph(
+        src=src_out, dst=dst_out, num_nodes=num_nodes, dst_rowptr=dst_rowptr, src_rowptr=src_rowptr,
+        edge_ids_by_src=edge_ids_by_src,
+        edge_ids_by_dst=torch.arange(num_edges, device=device, dtype=torch.int32),
+        node_order=node_order, source_node_order=source_node_order,
+        node_tiers=_node_tiers(dst_rowptr, node_order, num_nodes, num_edges, device),
+        source_segments=make_source_segments(src_rowptr),
+    )
+    return graph
+
+
+class _NullContext:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *args):
+        return False
+
+
+def _build_host(src, dst, num_nodes):
+    device = src.device
+
+    def rowptr(index_tensor):
+        out = torch.zeros(num_nodes + 1, dtype=torch.int32, device=device)
+        if index_tensor.numel():
+            counts = torch.bincount(index_tensor.long(), minlength=num_nodes)
+            out[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        return out
+
+    src_rowptr, dst_rowptr = rowptr(src), rowptr(dst)
+    node_order = torch.argsort(dst_rowptr.diff().long(), descending=True, stable=True).to(torch.int32)
+    source_node_order = torch.argsort(src_rowptr.diff().long(), descending=True, stable=True).to(torch.int32)
+    edge_ids_by_src = torch.argsort(src.long(), stable=True).to(torch.int32)
+    return (src.to(torch.int32, copy=True), dst.to(torch.int32, copy=True), dst_rowptr, src_rowptr, edge_ids_by_src,
+            node_order, source_node_order)
+
+
+def _build_cuda(src, dst, num_nodes):
+    lib = _native.library()
+    device = src.device
+    edges = src.numel()
+    i32 = dict(dtype=torch.int32, device=device)
+    out = [torch.empty(edges, **i32), torch.empty(edges, **i32), torch.empty(num_nodes + 1, **i32),
+           torch.empty(num_nodes + 1, **i32), torch.empty(edges, **i32), torch.empty(num_nodes, **i32),
+           torch.empty(num_nodes, **i32)]
+    with torch.cuda.device(device):
+        scratch_bytes = lib.luna_graph_scratch_bytes(num_nodes, edges)
+        scratch = torch.empty(max(scratch_bytes, 1), dtype=torch.uint8, device=device)
+        view = _native.GraphOut(*(t.data_ptr() for t in out))
+        bits = 64 if src.dtype == torch.int64 else 32
+        _native.check(lib.luna_graph_build(src.data_ptr(), dst.data_ptr(), bits, num_nodes, edges,
+                                           ctypes.byref(view), scratch.data_ptr(), scratch_bytes,
+                                           _native.current_stream(device)))
+    return tuple(out)
+
+
+__all__ = ["LunaTPGraph", "SourceSegmentTables", "make_graph", "make_source_segments"]

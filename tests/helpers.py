@@ -1,0 +1,76 @@
+"""Helpers shared by the parity tests: configurations, seeded problems and the reference's tolerance rule."""
+
+import torch
+
+from lunaequivariance_b200 import Irreps
+
+# (irreps_in1, irreps_in2, irreps_out, instructions or None for "all parity-allowed uvu paths", options)
+CONFIGS = {
+    "cfg1": ("32x1o", "1x1o", "32x0e", [(0, 0, 0, "uvu", True)], {}),
+    "cfg2": ("128x0e+128x1o+128x2e", "1x0e+1x1o+1x2e+1x3o", "128x0e+128x1o+128x2e+128x3o", None, {}),
+    "cfg4": ("64x0e+64x1o+64x2e+64x3o", "1x0e+1x1o+1x2e+1x3o", "64x0e+64x1o+64x2e+64x3o", None, {}),
+    "cfg5": ("64x0e+64x1o+64x2e", "1x0e+1x1o+1x2e", "64x0e+64x1o+64x2e", None, {}),
+    "fixture": ("32x0e+32x1o", "1x0e+1x1o", "32x0e+32x1o", None, {}),
+    "small": ("4x0e+4x1o+4x2e", "1x0e+1x1o+1x2e", "4x0e+4x1o+4x2e", None, {}),
+    "mul2": ("5x0e+5x1o", "2x0e+3x1o", "5x0e+5x1o", None, {}),
+    "odd": ("33x0e+33x1o", "1x0e+1x1o", "33x0e+33x1o", None, {}),
+    "one": ("1x0e+1x1o", "1x0e+1x1o", "1x0e+1x1o", None, {}),
+    "mixed": ("3x0e+3x1o+3x1e", "1x0e+1x1o", "3x0e+3x1o+3x1e+3x1o", None, {}),
+    "highl": ("3x5o", "2x5o", "3x0e+3x2e+3x4e", None, {}),
+    "partial": ("32x0e+32x1o", "1x0e+1x1o", "32x0e+32x1o+32x2e", [(0, 0, 0, "uvu", True), (1, 1, 0, "uvu", True),
+                                                                   (1, 1, 2, "uvu", True)], {}),
+    "wide": ("256x0e+256x1o", "1x0e+1x1o", "256x0e+256x1o", None, {}),
+    "norm_path": ("4x0e+4x1o", "1x0e+1x1o", "4x0e+4x1o", None,
+                  {"irrep_normalization": "norm", "path_normalization": "path"}),
+}
+
+
+def all_paths(in1, in2, out):
+    in1, in2, out = Irreps(in1), Irreps(in2), Irreps(out)
+    return [(i, j, k, "uvu", True)
+            for i, (_, a) in enumerate(in1) for j, (_, b) in enumerate(in2) for k, (_, c) in enumerate(out)
+            if c in a * b]
+
+
+def config(name):
+    in1, in2, out, instructions, options = CONFIGS[name]
+    if instructions is None:
+        instructions = all_paths(in1, in2, out)
+    return in1, in2, out, instructions, options
+
+
+def random_graph(nodes, edges, generator, exact_degree=None):
+    """Destination-sorted random edge list on CPU (int64)."""
+    if exact_degree is not None:
+        dst = torch.arange(nodes).repeat_interleave(exact_degree)
+        src = torch.randint(nodes - 1, (dst.numel(),), generator=generator)
+        src = src + (src >= dst).long()  # uniform over the other nodes
+        return src, dst
+    src = torch.randint(nodes, (edges,), generator=generator)
+    dst = torch.sort(torch.randint(nodes, (edges,), generator=generator))[0]
+    return src, dst
+
+
+def random_problem(meta_dims, nodes, src, dtype, generator):
+    in1_dim, in2_dim, out_dim, weight_numel = meta_dims
+    edges = src.numel()
+    rand = lambda *shape: torch.randn(*shape, generator=generator, dtype=torch.float64).to(dtype)
+    return dict(x=rand(nodes, in1_dim), y=rand(edges, in2_dim), w=rand(edges, weight_numel),
+                g=rand(nodes, out_dim), rx=rand(nodes, in1_dim), ry=rand(edges, in2_dim),
+                rw=rand(edges, weight_numel))
+
+
+def tolerance(dtype):
+    """north-star bound: 1e-5 relative in FP32, 1e-12 in FP64, relative to the largest reference magnitude
+    (the reference's rule, tests/testing_utils.py:14-41: max|a - r| <= atol + rtol * max|r|)."""
+    return 1e-5 if dtype == torch.float32 else 1e-12
+
+
+def assert_close(actual, expected, dtype, what=""):
+    expected = expected.to(torch.float64)
+    actual = actual.detach().to("cpu", torch.float64)
+    assert actual.shape == expected.shape, (what, actual.shape, expected.shape)
+    scale = max(expected.abs().max().item(), 1e-30) if expected.numel() else 1.0
+    error = (actual - expected).abs().max().item() if expected.numel() else 0.0
+    assert error <= tolerance(dtype) * scale + 1e-300, f"{what}: max error {error:.3e} vs scale {scale:.3e}"
+    return error / scale
