@@ -93,10 +93,10 @@ void analyse_fast(luna_uvu_plan* plan) {
   // paths sorted by (l1, l3)
   std::vector<int> order(paths.size());
   for (size_t i = 0; i < order.size(); ++i) order[i] = static_cast<int>(i);
-  const int LO1 = f.LO + 1;
+  const int LO1 = kMaxFastL + 1;  // fixed stride so kernels compiled for larger degrees index the same table
   auto pair_of = [&](int p) { return ((paths[p].d1 - 1) / 2) * LO1 + (paths[p].d3 - 1) / 2; };
   std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return pair_of(a) < pair_of(b); });
-  const int npairs = (f.LX + 1) * LO1;
+  const int npairs = LO1 * LO1;
   for (int i = 0; i <= npairs; ++i) f.pair_ptr[i] = 0;
   for (int p : order) f.pair_ptr[pair_of(p) + 1]++;
   for (int i = 0; i < npairs; ++i) f.pair_ptr[i + 1] += f.pair_ptr[i];

@@ -1,0 +1,178 @@
+// Building blocks of the staged kernels: mbarrier / bulk-copy wrappers (1-D TMA copies into this CTA's own shared
+// memory), small vector types, compile-time loops, the warp-wide lower-bound search that assigns contiguous node
+// ranges to warps, and the per-edge coupling-matrix computation.
+//
+// Formulation shared by all staged kernels.  For one edge e the edge attributes y[e] are the same for every
+// channel, so each path p is first reduced to a small dense matrix
+//     M^p[i][k] = sum_j C^p_ijk * y[e, j]                     (d1 x d3, computed once per edge by the warp)
+// and the per-channel work becomes dense:
+//     forward   out_k  += w_p * sum_i M^p[i][k] * x_i
+//     backward  gx_i   += sum_k M^p[i][k] * (w_p * g_k),   gw_p = sum_k g_k * sum_i M^p[i][k] x_i,
+//               G^p[i][k] = sum_channels x_i * (w_p * g_k)  and  gy_j = sum_p sum_ik C^p_ijk G^p[i][k].
+// The sparse coupling table is only touched in the per-edge (not per-channel) part, so the hot loops depend on the
+// degrees (d1, d3) alone and one compiled kernel serves every path list of a given shape class.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <type_traits>
+
+#include "plan.h"
+
+namespace luna {
+namespace fastk {
+
+constexpr int kWarps = 4;           // warps per CTA; each warp streams its own edge range
+constexpr int kMaxStages = 4;
+constexpr uint32_t kWaitLimit = 1u << 20;  // bounded mbarrier polling
+
+// ---- shared-memory barriers and bulk copies -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Polls with an iteration limit; returns false if the barrier never completed.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kWaitLimit; ++spin)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on an mbarrier.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// ---- small vectors ------------------------------------------------------------------------------------------------
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Vec {
+  T a[N];
+};
+
+// Loads NV vectors of CPL elements from p (aligned to the vector size) into flat[NV * CPL].
+template <typename T, int CPL, int NV>
+__device__ __forceinline__ void load_vectors(const T* p, T* flat) {
+  const Vec<T, CPL>* v = reinterpret_cast<const Vec<T, CPL>*>(p);
+#pragma unroll
+  for (int n = 0; n < NV; ++n) {
+    const Vec<T, CPL> t = v[n];
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) flat[n * CPL + c] = t.a[c];
+  }
+}
+template <typename T, int CPL, int NV>
+__device__ __forceinline__ void store_vectors(T* p, const T* flat) {
+  Vec<T, CPL>* v = reinterpret_cast<Vec<T, CPL>*>(p);
+#pragma unroll
+  for (int n = 0; n < NV; ++n) {
+    Vec<T, CPL> t;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) t.a[c] = flat[n * CPL + c];
+    v[n] = t;
+  }
+}
+// Streaming (evict-first) variant for write-once outputs such as gw.
+template <typename T, int CPL, int NV>
+__device__ __forceinline__ void store_vectors_streaming(T* p, const T* flat) {
+  Vec<T, CPL>* v = reinterpret_cast<Vec<T, CPL>*>(p);
+#pragma unroll
+  for (int n = 0; n < NV; ++n) {
+    Vec<T, CPL> t;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) t.a[c] = flat[n * CPL + c];
+    if constexpr (sizeof(T) * CPL == 16) {
+      __stcs(reinterpret_cast<float4*>(v + n), *reinterpret_cast<const float4*>(&t));
+    } else if constexpr (sizeof(T) * CPL == 8) {
+      __stcs(reinterpret_cast<float2*>(v + n), *reinterpret_cast<const float2*>(&t));
+    } else {
+      __stcs(reinterpret_cast<float*>(v + n), *reinterpret_cast<const float*>(&t));
+    }
+  }
+}
+
+// Reads a d1 x d3 matrix (row-major, 16-byte aligned, padded to a multiple of 16 bytes) from shared memory with
+// 128-bit loads; every lane reads the same address, so each load is one broadcast.
+template <typename T, int COUNT>
+__device__ __forceinline__ void load_matrix(const T* m, T* regs) {
+  constexpr int per = 16 / sizeof(T);
+  constexpr int nv = (COUNT + per - 1) / per;
+  const Vec<T, per>* v = reinterpret_cast<const Vec<T, per>*>(m);
+#pragma unroll
+  for (int n = 0; n < nv; ++n) {
+    const Vec<T, per> t = v[n];
+#pragma unroll
+    for (int c = 0; c < per; ++c)
+      if (n * per + c < COUNT) regs[n * per + c] = t.a[c];
+  }
+}
+
+// ---- compile-time loop ----------------------------------------------------------------------------------------------
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+
+// ---- work assignment ------------------------------------------------------------------------------------------------
+// First n in [0, count] with rowptr[n] >= bound (rowptr is ascending); all 32 lanes cooperate, 32-ary search.
+__device__ __forceinline__ int64_t warp_lower_bound(const int* __restrict__ rowptr, int64_t count, int64_t bound,
+                                                    int lane) {
+  int64_t lo = 0, hi = count;
+  while (hi - lo > 32) {
+    const int64_t step = (hi - lo + 31) / 32;
+    const int64_t idx = lo + step * lane;
+    const bool below = idx < hi && rowptr[idx] < bound;
+    const int cnt = __popc(__ballot_sync(0xffffffffu, below));
+    if (cnt == 0) {
+      hi = lo;
+    } else {
+      const int64_t new_hi = lo + step * cnt;
+      lo = lo + step * (cnt - 1) + 1;
+      hi = new_hi < hi ? new_hi : hi;
+    }
+  }
+  const int64_t idx = lo + lane;
+  const bool below = idx < hi && rowptr[idx] < bound;
+  return lo + __popc(__ballot_sync(0xffffffffu, below));
+}
+
+// ---- per-edge coupling matrices -------------------------------------------------------------------------------------
+// mbuf[m] = sum_t c[t] * ybuf[j[t]] over the CSR program; lanes stride over the entries.
+template <typename T>
+__device__ __forceinline__ void compute_m(const int* __restrict__ ptr, const int* __restrict__ jdx,
+                                          const T* __restrict__ coef, const T* ybuf, T* mbuf, int m_total, int lane) {
+  for (int m = lane; m < m_total; m += 32) {
+    const int t0 = __ldg(ptr + m), t1 = __ldg(ptr + m + 1);
+    T a = T(0);
+    for (int t = t0; t < t1; ++t) a = fma(__ldg(coef + t), ybuf[__ldg(jdx + t)], a);
+    mbuf[m] = a;
+  }
+}
+
+}  // namespace fastk
+}  // namespace luna

@@ -1,0 +1,237 @@
+// Staged forward-shaped kernel (free argument g):  out[t] = sum_{e: dst e = t} sum_p w_p * (M^p(y_e)^T x[src e]).
+//
+// One warp owns a contiguous range of destination nodes (balanced by edge count) and therefore a contiguous range
+// of the destination-sorted edge list: a warp-segmented reduction with register accumulators and no atomics.  Per
+// edge, one elected lane issues 1-D bulk copies (cp.async.bulk, completion on an mbarrier) of the edge's weight
+// row and of the gathered x[src] row into the warp's ring of shared-memory stages; the warp then reads them with
+// 128-bit shared loads while later edges are in flight.  A lane owns CPL consecutive channels of every block.
+#pragma once
+
+#include <algorithm>
+
+#include "uvu_fast.cuh"
+
+namespace luna {
+namespace fastk {
+
+template <typename T>
+struct FwdParams {
+  FastMeta meta;
+  const T* x;
+  const T* y;
+  const T* w;
+  T* out;
+  const int* src;
+  const int* dst_rowptr;
+  const int* m_ptr;
+  const int* m_j;
+  const T* m_c;
+  int* status;
+  int64_t num_nodes, num_edges;
+  int stages;
+  int accumulate;
+};
+
+template <typename T>
+__host__ __device__ inline size_t fwd_warp_bytes(const FastMeta& f, int stages) {
+  const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
+  return stages * stage + static_cast<size_t>(f.m_total) * sizeof(T) + 32 * sizeof(T) + kMaxStages * sizeof(uint64_t);
+}
+
+template <typename T, int CPL, int LX, int LO>
+__global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_constant__ FwdParams<T> P) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const FastMeta& F = P.meta;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int stages = P.stages;
+  const int stage_elems = F.w_stage_elems + F.x_stage_elems;
+  unsigned char* base = smem_raw + static_cast<size_t>(warp) * fwd_warp_bytes<T>(F, stages);
+  T* stage_mem = reinterpret_cast<T*>(base);
+  T* mbuf = stage_mem + static_cast<size_t>(stages) * stage_elems;
+  T* ybuf = mbuf + F.m_total;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ybuf + 32);
+
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&bars[s], 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+
+  const int chw = 32 * CPL;
+  const int c0 = blockIdx.y * chw;  // first channel of this warp's chunk
+  const int64_t E = P.num_edges, N = P.num_nodes;
+  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kWarps;
+  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  const int64_t bound_lo = E * gwarp / total_warps, bound_hi = E * (gwarp + 1) / total_warps;
+  const int64_t n_lo = warp_lower_bound(P.dst_rowptr, N, bound_lo, lane);
+  const int64_t n_hi = gwarp == total_warps - 1 ? N : warp_lower_bound(P.dst_rowptr, N, bound_hi, lane);
+  if (n_lo >= n_hi) return;
+  const int64_t e_begin = P.dst_rowptr[n_lo], e_end = P.dst_rowptr[n_hi];
+
+  const uint32_t stage_bytes = static_cast<uint32_t>(stage_elems * sizeof(T));
+  const int n_pieces = F.n_w_pieces + F.n_x_pieces;
+  auto issue = [&](int64_t e, int s) {
+    uint64_t* bar = &bars[s];
+    if (lane == 0) mbar_arrive_expect_tx(bar, stage_bytes);
+    __syncwarp();
+    T* dst = stage_mem + static_cast<size_t>(s) * stage_elems;
+    for (int pi = lane; pi < n_pieces; pi += 32) {
+      if (pi < F.n_w_pieces) {
+        const CopyPiece pc = F.pieces_w[pi];
+        bulk_copy_g2s(dst + pc.s_off, P.w + e * F.W + pc.g_off + c0 * pc.comp,
+                      static_cast<uint32_t>(pc.n * sizeof(T)), bar);
+      } else {
+        const CopyPiece pc = F.pieces_x[pi - F.n_w_pieces];
+        const int64_t s_node = P.src[e];
+        bulk_copy_g2s(dst + F.w_stage_elems + pc.s_off, P.x + s_node * F.X + pc.g_off + c0 * pc.comp,
+                      static_cast<uint32_t>(pc.n * sizeof(T)), bar);
+      }
+    }
+  };
+
+  for (int s = 0; s < stages; ++s)
+    if (e_begin + s < e_end) issue(e_begin + s, s);
+
+  T y_next = (lane < F.Y && e_begin < e_end) ? P.y[e_begin * F.Y + lane] : T(0);
+  constexpr int XR = (LX + 1) * (LX + 1) * CPL;
+  constexpr int AR = (LO + 1) * (LO + 1) * CPL;
+  T acc[AR];
+  int64_t e = e_begin;
+  uint32_t it = 0;
+  bool alive = true;
+
+  for (int64_t n = n_lo; n < n_hi && alive; ++n) {
+    const int64_t ee = P.dst_rowptr[n + 1];
+#pragma unroll
+    for (int a = 0; a < AR; ++a) acc[a] = T(0);
+    for (; e < ee; ++e, ++it) {
+      const int s = it % stages;
+      const uint32_t parity = (it / stages) & 1u;
+      if (!mbar_wait_bounded(&bars[s], parity)) {
+        if (lane == 0) atomicExch(P.status, 1);
+        alive = false;
+        break;
+      }
+      const T* ws = stage_mem + static_cast<size_t>(s) * stage_elems;
+      const T* xs = ws + F.w_stage_elems;
+      // coupling matrices of this edge
+      if (lane < F.Y) ybuf[lane] = y_next;
+      __syncwarp();
+      compute_m<T>(P.m_ptr, P.m_j, P.m_c, ybuf, mbuf, F.m_total, lane);
+      if (e + 1 < e_end && lane < F.Y) y_next = P.y[(e + 1) * F.Y + lane];
+      __syncwarp();
+      // this lane's channels of the gathered x row
+      T xr[XR];
+      static_for<0, LX + 1>([&](auto l1c) {
+        constexpr int l1 = decltype(l1c)::value;
+        constexpr int d1 = 2 * l1 + 1;
+        if (F.x_off[l1] >= 0) load_vectors<T, CPL, d1>(xs + F.xs_off[l1] + lane * (CPL * d1), &xr[l1 * l1 * CPL]);
+      });
+      static_for<0, LX + 1>([&](auto l1c) {
+        constexpr int l1 = decltype(l1c)::value;
+        constexpr int d1 = 2 * l1 + 1;
+        static_for<0, LO + 1>([&](auto l3c) {
+          constexpr int l3 = decltype(l3c)::value;
+          constexpr int d3 = 2 * l3 + 1;
+          const int q_end = F.pair_ptr[l1 * (kMaxFastL + 1) + l3 + 1];
+          for (int q = F.pair_ptr[l1 * (kMaxFastL + 1) + l3]; q < q_end; ++q) {
+            T wv[CPL];
+            load_vectors<T, CPL, 1>(ws + F.w_soff[q] + lane * CPL, wv);
+            T mr[d1 * d3];
+            load_matrix<T, d1 * d3>(mbuf + F.m_off[q], mr);
+            const T* xl = &xr[l1 * l1 * CPL];
+            T* al = &acc[l3 * l3 * CPL];
+#pragma unroll
+            for (int c = 0; c < CPL; ++c) {
+#pragma unroll
+              for (int k = 0; k < d3; ++k) {
+                T t = mr[k] * xl[c * d1];
+#pragma unroll
+                for (int i = 1; i < d1; ++i) t = fma(mr[i * d3 + k], xl[c * d1 + i], t);
+                al[c * d3 + k] = fma(wv[c], t, al[c * d3 + k]);
+              }
+            }
+          }
+        });
+      });
+      __syncwarp();  // every lane is done with this stage, mbuf and ybuf
+      if (e + stages < e_end) issue(e + stages, s);
+    }
+    if (!alive) break;
+    // flush the node's accumulators
+    static_for<0, LO + 1>([&](auto l3c) {
+      constexpr int l3 = decltype(l3c)::value;
+      constexpr int d3 = 2 * l3 + 1;
+      if (F.o_off[l3] >= 0) {
+        T* dst = P.out + n * F.O + F.o_off[l3] + c0 * d3 + lane * (CPL * d3);
+        T* al = &acc[l3 * l3 * CPL];
+        if (P.accumulate) {
+          T old[CPL * d3];
+          load_vectors<T, CPL, d3>(dst, old);
+#pragma unroll
+          for (int a = 0; a < CPL * d3; ++a) al[a] += old[a];
+        }
+        store_vectors<T, CPL, d3>(dst, al);
+      }
+    });
+  }
+  if (!alive) {
+    // let copies that are still in flight land before the CTA's shared memory is released
+    for (int d = 1; d < stages; ++d)
+      if (e + d < e_end) mbar_wait_bounded(&bars[(it + d) % stages], ((it + d) / stages) & 1u);
+  }
+}
+
+// Host side: picks the stage count, sets the shared-memory attribute, launches.
+int choose_stages(size_t stage_bytes, size_t fixed_bytes, int max_smem_optin, size_t* block_bytes);
+
+template <typename T, int CPL, int LX, int LO>
+int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
+                        const T* y, const T* w, T* out, bool accumulate, cudaStream_t stream) {
+  const FastMeta& f = plan->fast;
+  FwdParams<T> P;
+  P.meta = f;
+  P.x = x;
+  P.y = y;
+  P.w = w;
+  P.out = out;
+  P.src = graph->src;
+  P.dst_rowptr = graph->dst_rowptr;
+  P.m_ptr = dt.m_ptr;
+  P.m_j = dt.m_j;
+  P.m_c = static_cast<const T*>(dt.m_c);
+  P.status = dt.status;
+  P.num_nodes = graph->num_nodes;
+  P.num_edges = graph->num_edges;
+  P.accumulate = accumulate ? 1 : 0;
+  const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
+  const size_t fixed = static_cast<size_t>(f.m_total) * sizeof(T) + 32 * sizeof(T) + kMaxStages * sizeof(uint64_t);
+  size_t block_bytes = 0;
+  P.stages = choose_stages(stage, fixed, dt.max_smem_optin, &block_bytes);
+  if (P.stages == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged forward needs more shared memory than the device has");
+  auto kernel = fast_fwd_kernel<T, CPL, LX, LO>;
+  LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
+  // about 512 edges per warp, rounded to whole waves of two CTAs per SM
+  int64_t warps = std::max<int64_t>(1, ceil_div(graph->num_edges, 512));
+  int64_t blocks = ceil_div(warps, kWarps);
+  const int64_t wave = static_cast<int64_t>(dt.sm_count) * 2;
+  if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
+  const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
+  kernel<<<grid, kWarps * 32, block_bytes, stream>>>(P);
+  LUNA_LAUNCH_CHECK("staged forward");
+  return LUNA_OK;
+}
+
+// Dispatch on the degree class: the smallest compiled (LX, LO) that covers the plan.
+template <typename T, int CPL>
+int launch_fast_fwd(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
+                    const T* y, const T* w, T* out, bool accumulate, cudaStream_t stream) {
+  const int lx = plan->fast.LX, lo = plan->fast.LO;
+  if (lx <= 1 && lo <= 1) return launch_fast_fwd_one<T, CPL, 1, 1>(plan, dt, graph, x, y, w, out, accumulate, stream);
+  if (lx <= 2 && lo <= 2) return launch_fast_fwd_one<T, CPL, 2, 2>(plan, dt, graph, x, y, w, out, accumulate, stream);
+  if (lx <= 2 && lo <= 3) return launch_fast_fwd_one<T, CPL, 2, 3>(plan, dt, graph, x, y, w, out, accumulate, stream);
+  return launch_fast_fwd_one<T, CPL, 3, 3>(plan, dt, graph, x, y, w, out, accumulate, stream);
+}
+
+}  // namespace fastk
+}  // namespace luna
