@@ -99,11 +99,14 @@ LUNA_API int luna_uvu_plan_set_generic(luna_uvu_plan* plan, int force_generic);
  * (src/lunatp/graph.py:17-33): int32 endpoints, CSR by destination and by source, and the permutation that
  * lists edge ids grouped by source. */
 typedef struct {
-  int64_t num_nodes, num_edges;
-  const int32_t* src;             /* [E] */
-  const int32_t* dst;             /* [E] ascending */
-  const int32_t* dst_rowptr;      /* [N+1] */
-  const int32_t* src_rowptr;      /* [N+1] */
+  int64_t num_nodes;     /* destination rows: out, g are [num_nodes, out_dim] */
+  int64_t num_src_nodes; /* source rows: x, gx are [num_src_nodes, in1_dim]; 0 means "same as num_nodes".  Differs
+                            when a rank holds a destination range of a partitioned graph. */
+  int64_t num_edges;
+  const int32_t* src;             /* [E] source row of each edge */
+  const int32_t* dst;             /* [E] ascending destination row */
+  const int32_t* dst_rowptr;      /* [num_nodes+1] */
+  const int32_t* src_rowptr;      /* [num_src_nodes+1] */
   const int32_t* edge_ids_by_src; /* [E] */
 } luna_graph;
 
@@ -134,25 +137,27 @@ LUNA_API int luna_uvu_conv_dbl_bwd(luna_uvu_plan* plan, const luna_graph* graph,
 LUNA_API int luna_uvu_check_status(luna_uvu_plan* plan, void* stream);
 
 /* --------------------------------------------------------------------------------------------------------------
- * Graph tables.  Replaces make_graph_tables (src/lunatp/utils/graph.py:637-764) for int32 tables.
- * Inputs src/dst are int32 or int64 device arrays (index_bits 32/64), dst ascending.  The call validates
- * (negative index, unsorted dst, index >= num_nodes) and reports through *host_status (a host int the call
- * writes after synchronising the stream): 0 ok, 1 negative index, 2 unsorted dst, 3 index out of range.
- * required_nodes receives max index + 1. */
+ * Graph tables.  Replaces make_graph_tables / graph_bounds (src/lunatp/utils/graph.py:637-838) for int32
+ * tables.  Inputs src/dst are int32 or int64 device arrays (index_bits 32/64), dst ascending.
+ * luna_graph_bounds scans the edge list and returns, after synchronising the stream, the smallest and largest
+ * index of src and of dst and whether dst is unsorted (the caller raises the reference's errors from these).
+ * luna_graph_build fills the tables; it trusts the bounds (indices inside [0, num_nodes) / [0, num_src_nodes)). */
 typedef struct {
   int32_t* src;               /* [E] */
   int32_t* dst;               /* [E] */
-  int32_t* dst_rowptr;        /* [N+1] */
-  int32_t* src_rowptr;        /* [N+1] */
+  int32_t* dst_rowptr;        /* [num_nodes+1] */
+  int32_t* src_rowptr;        /* [num_src_nodes+1] */
   int32_t* edge_ids_by_src;   /* [E] stable by source */
-  int32_t* node_order;        /* [N] in-degree descending, stable */
-  int32_t* source_node_order; /* [N] out-degree descending, stable */
+  int32_t* node_order;        /* [num_nodes] in-degree descending, stable */
+  int32_t* source_node_order; /* [num_src_nodes] out-degree descending, stable */
 } luna_graph_out;
 LUNA_API int64_t luna_graph_scratch_bytes(int64_t num_nodes, int64_t num_edges);
 LUNA_API int luna_graph_bounds(const void* src, const void* dst, int index_bits, int64_t num_edges, int64_t* min_index,
-                      int64_t* max_index, int* unsorted, void* scratch, int64_t scratch_bytes, void* stream);
-LUNA_API int luna_graph_build(const void* src, const void* dst, int index_bits, int64_t num_nodes, int64_t num_edges,
-                     const luna_graph_out* out, void* scratch, int64_t scratch_bytes, void* stream);
+                      int64_t* max_src, int64_t* max_dst, int* unsorted, void* scratch, int64_t scratch_bytes,
+                      void* stream);
+LUNA_API int luna_graph_build(const void* src, const void* dst, int index_bits, int64_t num_nodes, int64_t num_src_nodes,
+                     int64_t num_edges, const luna_graph_out* out, void* scratch, int64_t scratch_bytes,
+                     void* stream);
 
 /* --------------------------------------------------------------------------------------------------------------
  * Real spherical harmonics (e3nn convention), degrees <= 12.  v[n,3] -> out[n, sum(2l+1)] for the listed

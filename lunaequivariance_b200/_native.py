@@ -56,7 +56,7 @@ class UvuDesc(ctypes.Structure):
 
 class Graph(ctypes.Structure):
     _fields_ = [
-        ("num_nodes", ctypes.c_int64), ("num_edges", ctypes.c_int64),
+        ("num_nodes", ctypes.c_int64), ("num_src_nodes", ctypes.c_int64), ("num_edges", ctypes.c_int64),
         ("src", ctypes.c_void_p), ("dst", ctypes.c_void_p), ("dst_rowptr", ctypes.c_void_p),
         ("src_rowptr", ctypes.c_void_p), ("edge_ids_by_src", ctypes.c_void_p),
     ]
@@ -93,9 +93,9 @@ _SIGNATURES = {
     "luna_uvu_check_status": (ctypes.c_int, [_P, _P]),
     "luna_graph_scratch_bytes": (ctypes.c_int64, [ctypes.c_int64, ctypes.c_int64]),
     "luna_graph_bounds": (ctypes.c_int, [_P, _P, ctypes.c_int, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64),
-                                         ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int), _P,
-                                         ctypes.c_int64, _P]),
-    "luna_graph_build": (ctypes.c_int, [_P, _P, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                                         ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
+                                         ctypes.POINTER(ctypes.c_int), _P, ctypes.c_int64, _P]),
+    "luna_graph_build": (ctypes.c_int, [_P, _P, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                         ctypes.POINTER(GraphOut), _P, ctypes.c_int64, _P]),
     "luna_sh_fwd": (ctypes.c_int, [ctypes.POINTER(ShDesc), _P, _P, ctypes.c_int64, _P]),
     "luna_sh_bwd": (ctypes.c_int, [ctypes.POINTER(ShDesc), _P, _P, _P, ctypes.c_int64, _P]),

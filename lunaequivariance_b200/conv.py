@@ -199,9 +199,9 @@ def _prepared(tensor: torch.Tensor | None) -> torch.Tensor | None:
     return tensor
 
 
-def _check_inputs(op: LunaTPUVUConv, x, y, w, num_nodes, num_edges) -> None:
+def _check_inputs(op: LunaTPUVUConv, x, y, w, source_rows, num_edges) -> None:
     _require_cuda(x)
-    for name, t, rows, cols in (("x", x, num_nodes, op.in1_dim), ("edge_attr", y, num_edges, op.in2_dim),
+    for name, t, rows, cols in (("x", x, source_rows, op.in1_dim), ("edge_attr", y, num_edges, op.in2_dim),
                                 ("weight", w, num_edges, op.weight_numel)):
         if t.dtype != op.compute_dtype:
             raise TypeError(f"{name} must be {op.compute_dtype}, got {t.dtype}")
@@ -228,20 +228,22 @@ class _GraphView:
             if t.dtype != torch.int32:
                 raise OverflowError("this build supports int32 graph tables only")
         self.num_nodes = int(num_nodes)
+        self.source_rows = int(src_rowptr.numel()) - 1
         self.num_edges = int(src.numel())
-        self.struct = _native.Graph(self.num_nodes, self.num_edges, src.data_ptr(), dst.data_ptr(),
+        self.struct = _native.Graph(self.num_nodes, self.source_rows, self.num_edges, src.data_ptr(), dst.data_ptr(),
                                     dst_rowptr.data_ptr(), src_rowptr.data_ptr(), edge_ids_by_src.data_ptr())
 
 
 def _graph_struct(graph):
+    """(native struct, destination rows, source rows, edges)"""
     if isinstance(graph, LunaTPGraph):
-        return graph.native(), graph.num_nodes, graph.num_edges
-    return graph.struct, graph.num_nodes, graph.num_edges
+        return graph.native(), graph.num_nodes, graph.source_rows, graph.num_edges
+    return graph.struct, graph.num_nodes, graph.source_rows, graph.num_edges
 
 
 def run_forward(op: LunaTPUVUConv, x, y, w, graph) -> torch.Tensor:
-    struct, n, e = _graph_struct(graph)
-    _check_inputs(op, x, y, w, n, e)
+    struct, n, ns, e = _graph_struct(graph)
+    _check_inputs(op, x, y, w, ns, e)
     x, y, w = _prepared(x), _prepared(y), _prepared(w)
     out = torch.empty((n, op.out_dim), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
@@ -252,8 +254,8 @@ def run_forward(op: LunaTPUVUConv, x, y, w, graph) -> torch.Tensor:
 
 
 def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True)):
-    struct, n, e = _graph_struct(graph)
-    _check_inputs(op, x, y, w, n, e)
+    struct, n, ns, e = _graph_struct(graph)
+    _check_inputs(op, x, y, w, ns, e)
     x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
     gx = torch.empty_like(x) if needs[0] else None
     gy = torch.empty_like(y) if needs[1] else None
@@ -270,8 +272,8 @@ def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True))
 
 
 def run_double_backward(op: LunaTPUVUConv, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True)):
-    struct, n, e = _graph_struct(graph)
-    _check_inputs(op, x, y, w, n, e)
+    struct, n, ns, e = _graph_struct(graph)
+    _check_inputs(op, x, y, w, ns, e)
     x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
     rx, ry, rw = _prepared(rx), _prepared(ry), _prepared(rw)
     hx = torch.empty_like(x) if needs[0] else None

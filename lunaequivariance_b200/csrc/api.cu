@@ -10,12 +10,15 @@ using namespace luna;
 namespace {
 
 size_t elem_size(const luna_uvu_plan* plan) { return plan->dtype == LUNA_F64 ? 8 : 4; }
+int64_t src_rows(const luna_graph* graph) { return graph->num_src_nodes > 0 ? graph->num_src_nodes : graph->num_nodes; }
 
 int check_common(const luna_uvu_plan* plan, const luna_graph* graph) {
   if (!plan) return fail(LUNA_ERR_INVALID_ARGUMENT, "null plan");
   if (!graph) return fail(LUNA_ERR_INVALID_ARGUMENT, "null graph");
-  if (graph->num_nodes < 0 || graph->num_edges < 0) return fail(LUNA_ERR_INVALID_ARGUMENT, "negative graph size");
-  if (graph->num_nodes >= (1LL << 31) - 1024 || graph->num_edges >= (1LL << 31) - 1024)
+  if (graph->num_nodes < 0 || graph->num_edges < 0 || graph->num_src_nodes < 0)
+    return fail(LUNA_ERR_INVALID_ARGUMENT, "negative graph size");
+  if (graph->num_nodes >= (1LL << 31) - 1024 || graph->num_src_nodes >= (1LL << 31) - 1024 ||
+      graph->num_edges >= (1LL << 31) - 1024)
     return fail(LUNA_ERR_OVERFLOW, "graph exceeds the 32-bit index range of this build");
   if (graph->num_nodes > 0 && (!graph->dst_rowptr || !graph->src_rowptr))
     return fail(LUNA_ERR_INVALID_ARGUMENT, "graph row pointers missing");
@@ -100,7 +103,7 @@ extern "C" int luna_uvu_conv_bwd(luna_uvu_plan* plan, const luna_graph* graph, c
   LUNA_TRY(check_ptr(plan, gx, "gx", false, 0));
   LUNA_TRY(check_ptr(plan, gy, "gy", false, 0));
   LUNA_TRY(check_ptr(plan, gw, "gw", false, 0));
-  if (E == 0 || N == 0) return zero_fill(gx, N * plan->X, elem_size(plan), stream);
+  if (E == 0 || N == 0) return zero_fill(gx, src_rows(graph) * plan->X, elem_size(plan), stream);
   if (use_fast(plan, {x, w, g, gx, gw}))
     return fast_backward(plan, graph, x, y, w, g, gx, false, gy, false, gw, false, scratch, scratch_bytes, stream);
   if (gx) LUNA_TRY(generic_contract(plan, graph, kFreeX, nullptr, y, w, g, gx, false, stream));
@@ -126,7 +129,7 @@ extern "C" int luna_uvu_conv_dbl_bwd(luna_uvu_plan* plan, const luna_graph* grap
                          {hy, "hy"}, {hw, "hw"}, {hg, "hg"}})
     LUNA_TRY(check_ptr(plan, p, name, false, 0));
   if (E == 0 || N == 0) {
-    LUNA_TRY(zero_fill(hx, N * plan->X, es, stream));
+    LUNA_TRY(zero_fill(hx, src_rows(graph) * plan->X, es, stream));
     return zero_fill(hg, N * plan->O, es, stream);
   }
   const bool fast = use_fast(plan, {x, w, g, rx, rw, hx, hw, hg});
@@ -162,7 +165,7 @@ extern "C" int luna_uvu_conv_dbl_bwd(luna_uvu_plan* plan, const luna_graph* grap
       ax = hx != nullptr;
       ay = hy != nullptr;
     }
-    if (hx && !ax) LUNA_TRY(zero_fill(hx, N * plan->X, es, stream));
+    if (hx && !ax) LUNA_TRY(zero_fill(hx, src_rows(graph) * plan->X, es, stream));
     if (hy && !ay) LUNA_TRY(zero_fill(hy, E * plan->Y, es, stream));
     if (hw && !aw) LUNA_TRY(zero_fill(hw, E * plan->W, es, stream));
     return LUNA_OK;
@@ -171,7 +174,7 @@ extern "C" int luna_uvu_conv_dbl_bwd(luna_uvu_plan* plan, const luna_graph* grap
     bool acc = false;
     if (ry) { LUNA_TRY(generic_contract(plan, graph, kFreeX, nullptr, ry, w, g, hx, acc, stream)); acc = true; }
     if (rw) { LUNA_TRY(generic_contract(plan, graph, kFreeX, nullptr, y, rw, g, hx, acc, stream)); acc = true; }
-    if (!acc) LUNA_TRY(zero_fill(hx, N * plan->X, es, stream));
+    if (!acc) LUNA_TRY(zero_fill(hx, src_rows(graph) * plan->X, es, stream));
   }
   if (hy) {
     bool acc = false;

@@ -13,7 +13,8 @@ constexpr int kThreads = 256;
 
 struct Bounds {
   long long min_index;
-  long long max_index;
+  long long max_src;
+  long long max_dst;
   int unsorted;
   int pad;
 };
@@ -21,30 +22,34 @@ struct Bounds {
 template <typename Index>
 __global__ void bounds_kernel(const Index* __restrict__ src, const Index* __restrict__ dst, int64_t edges,
                               Bounds* __restrict__ result) {
-  long long lo = INT64_MAX, hi = INT64_MIN;
+  long long lo = INT64_MAX, hi_s = INT64_MIN, hi_d = INT64_MIN;
   int unsorted = 0;
   for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < edges;
        e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const long long s = src[e], d = dst[e];
     lo = min(lo, min(s, d));
-    hi = max(hi, max(s, d));
+    hi_s = max(hi_s, s);
+    hi_d = max(hi_d, d);
     if (e > 0 && dst[e - 1] > d) unsorted = 1;
   }
   for (int offset = 16; offset > 0; offset >>= 1) {
     lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, offset));
-    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, offset));
+    hi_s = max(hi_s, __shfl_xor_sync(0xffffffffu, hi_s, offset));
+    hi_d = max(hi_d, __shfl_xor_sync(0xffffffffu, hi_d, offset));
     unsorted |= __shfl_xor_sync(0xffffffffu, unsorted, offset);
   }
   if ((threadIdx.x & 31) == 0) {
     atomicMin(&result->min_index, lo);
-    atomicMax(&result->max_index, hi);
+    atomicMax(&result->max_src, hi_s);
+    atomicMax(&result->max_dst, hi_d);
     if (unsorted) atomicOr(&result->unsorted, 1);
   }
 }
 
 __global__ void init_bounds(Bounds* result) {
   result->min_index = INT64_MAX;
-  result->max_index = INT64_MIN;
+  result->max_src = INT64_MIN;
+  result->max_dst = INT64_MIN;
   result->unsorted = 0;
 }
 
@@ -119,12 +124,12 @@ extern "C" int64_t luna_graph_scratch_bytes(int64_t num_nodes, int64_t num_edges
 }
 
 extern "C" int luna_graph_bounds(const void* src, const void* dst, int index_bits, int64_t num_edges,
-                                 int64_t* min_index, int64_t* max_index, int* unsorted, void* scratch,
-                                 int64_t scratch_bytes, void* stream_) {
+                                 int64_t* min_index, int64_t* max_src, int64_t* max_dst, int* unsorted,
+                                 void* scratch, int64_t scratch_bytes, void* stream_) {
   clear_error();
-  if (!min_index || !max_index || !unsorted) return fail(LUNA_ERR_INVALID_ARGUMENT, "null result pointer");
+  if (!min_index || !max_src || !max_dst || !unsorted) return fail(LUNA_ERR_INVALID_ARGUMENT, "null result pointer");
   *min_index = 0;
-  *max_index = -1;
+  *max_src = *max_dst = -1;
   *unsorted = 0;
   if (num_edges == 0) return LUNA_OK;
   if (!src || !dst) return fail(LUNA_ERR_INVALID_ARGUMENT, "null edge list");
@@ -146,26 +151,28 @@ extern "C" int luna_graph_bounds(const void* src, const void* dst, int index_bit
   LUNA_CUDA_CHECK(cudaMemcpyAsync(&host, result, sizeof(Bounds), cudaMemcpyDeviceToHost, stream));
   LUNA_CUDA_CHECK(cudaStreamSynchronize(stream));
   *min_index = host.min_index;
-  *max_index = host.max_index;
+  *max_src = host.max_src;
+  *max_dst = host.max_dst;
   *unsorted = host.unsorted;
   return LUNA_OK;
 }
 
 extern "C" int luna_graph_build(const void* src, const void* dst, int index_bits, int64_t num_nodes,
-                                int64_t num_edges, const luna_graph_out* out, void* scratch, int64_t scratch_bytes,
-                                void* stream_) {
+                                int64_t num_src_nodes, int64_t num_edges, const luna_graph_out* out, void* scratch,
+                                int64_t scratch_bytes, void* stream_) {
   clear_error();
   if (!out) return fail(LUNA_ERR_INVALID_ARGUMENT, "null output table set");
+  if (num_src_nodes <= 0) num_src_nodes = num_nodes;
   if (num_nodes < 0 || num_edges < 0) return fail(LUNA_ERR_INVALID_ARGUMENT, "negative graph size");
-  if (num_nodes >= (1LL << 31) - 1024 || num_edges >= (1LL << 31) - 1024)
+  if (std::max(num_nodes, num_src_nodes) >= (1LL << 31) - 1024 || num_edges >= (1LL << 31) - 1024)
     return fail(LUNA_ERR_OVERFLOW, "graph exceeds the 32-bit index range of this build");
   if (index_bits != 32 && index_bits != 64) return fail(LUNA_ERR_INVALID_ARGUMENT, "index_bits must be 32 or 64");
   if (!out->dst_rowptr || !out->src_rowptr) return fail(LUNA_ERR_INVALID_ARGUMENT, "row pointer outputs missing");
   if (num_edges > 0 && (!src || !dst || !out->src || !out->dst || !out->edge_ids_by_src))
     return fail(LUNA_ERR_INVALID_ARGUMENT, "edge tables missing");
-  if (num_nodes > 0 && (!out->node_order || !out->source_node_order))
+  if ((num_nodes > 0 && !out->node_order) || (num_src_nodes > 0 && !out->source_node_order))
     return fail(LUNA_ERR_INVALID_ARGUMENT, "node order outputs missing");
-  const ScratchLayout l = layout(num_nodes, num_edges);
+  const ScratchLayout l = layout(std::max(num_nodes, num_src_nodes), num_edges);
   if (!scratch || scratch_bytes < static_cast<int64_t>(l.total))
     return fail(LUNA_ERR_SCRATCH, "scratch too small: need %zu bytes", l.total);
   auto stream = static_cast<cudaStream_t>(stream_);
@@ -176,7 +183,7 @@ extern "C" int luna_graph_build(const void* src, const void* dst, int index_bits
   void* cub_temp = base + l.cub_temp;
   size_t cub_bytes = l.cub_bytes;
 
-  LUNA_CUDA_CHECK(cudaMemsetAsync(out->src_rowptr, 0, (num_nodes + 1) * sizeof(int32_t), stream));
+  LUNA_CUDA_CHECK(cudaMemsetAsync(out->src_rowptr, 0, (num_src_nodes + 1) * sizeof(int32_t), stream));
   LUNA_CUDA_CHECK(cudaMemsetAsync(out->dst_rowptr, 0, (num_nodes + 1) * sizeof(int32_t), stream));
   if (num_edges > 0) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(num_edges, kThreads));
@@ -193,27 +200,23 @@ extern "C" int luna_graph_build(const void* src, const void* dst, int index_bits
     LUNA_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(cub_temp, cub_bytes, static_cast<const int32_t*>(out->src),
                                                     keys_out, static_cast<const int32_t*>(values_in),
                                                     out->edge_ids_by_src, num_edges, 0,
-                                                    bits_for(std::max<int64_t>(num_nodes - 1, 1)), stream));
+                                                    bits_for(std::max<int64_t>(num_src_nodes - 1, 1)), stream));
   }
-  if (num_nodes > 0) {
+  const int degree_bits = bits_for(std::max<int64_t>(num_edges, 1));
+  for (int pass = 0; pass < 2; ++pass) {
+    const int64_t rows = pass == 0 ? num_nodes : num_src_nodes;
+    int32_t* rowptr = pass == 0 ? out->dst_rowptr : out->src_rowptr;
+    int32_t* order = pass == 0 ? out->node_order : out->source_node_order;
+    if (rows == 0) continue;
     cub_bytes = l.cub_bytes;
-    LUNA_CUDA_CHECK(cub::DeviceScan::InclusiveSum(cub_temp, cub_bytes, out->src_rowptr, out->src_rowptr,
-                                                  num_nodes + 1, stream));
+    LUNA_CUDA_CHECK(cub::DeviceScan::InclusiveSum(cub_temp, cub_bytes, rowptr, rowptr, rows + 1, stream));
+    degrees_and_iota<<<static_cast<unsigned>(ceil_div(rows, kThreads)), kThreads, 0, stream>>>(rowptr, rows, keys_in,
+                                                                                              values_in);
+    LUNA_LAUNCH_CHECK("graph degrees");
     cub_bytes = l.cub_bytes;
-    LUNA_CUDA_CHECK(cub::DeviceScan::InclusiveSum(cub_temp, cub_bytes, out->dst_rowptr, out->dst_rowptr,
-                                                  num_nodes + 1, stream));
-    const unsigned blocks = static_cast<unsigned>(ceil_div(num_nodes, kThreads));
-    const int degree_bits = bits_for(std::max<int64_t>(num_edges, 1));
-    for (int pass = 0; pass < 2; ++pass) {
-      const int32_t* rowptr = pass == 0 ? out->dst_rowptr : out->src_rowptr;
-      int32_t* order = pass == 0 ? out->node_order : out->source_node_order;
-      degrees_and_iota<<<blocks, kThreads, 0, stream>>>(rowptr, num_nodes, keys_in, values_in);
-      LUNA_LAUNCH_CHECK("graph degrees");
-      cub_bytes = l.cub_bytes;
-      LUNA_CUDA_CHECK(cub::DeviceRadixSort::SortPairsDescending(
-          cub_temp, cub_bytes, static_cast<const int32_t*>(keys_in), keys_out,
-          static_cast<const int32_t*>(values_in), order, num_nodes, 0, degree_bits, stream));
-    }
+    LUNA_CUDA_CHECK(cub::DeviceRadixSort::SortPairsDescending(
+        cub_temp, cub_bytes, static_cast<const int32_t*>(keys_in), keys_out, static_cast<const int32_t*>(values_in),
+        order, rows, 0, degree_bits, stream));
   }
   return LUNA_OK;
 }

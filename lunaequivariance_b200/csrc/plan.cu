@@ -90,11 +90,11 @@ void analyse_fast(luna_uvu_plan* plan) {
   f.W = plan->W;
   f.num_paths = static_cast<int>(paths.size());
 
-  // paths sorted by (l1, l3)
+  // paths sorted by (l3, l1): all paths into one output degree are contiguous, also in the M buffer
   std::vector<int> order(paths.size());
   for (size_t i = 0; i < order.size(); ++i) order[i] = static_cast<int>(i);
   const int LO1 = kMaxFastL + 1;  // fixed stride so kernels compiled for larger degrees index the same table
-  auto pair_of = [&](int p) { return ((paths[p].d1 - 1) / 2) * LO1 + (paths[p].d3 - 1) / 2; };
+  auto pair_of = [&](int p) { return ((paths[p].d3 - 1) / 2) * LO1 + (paths[p].d1 - 1) / 2; };
   std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return pair_of(a) < pair_of(b); });
   const int npairs = LO1 * LO1;
   for (int i = 0; i <= npairs; ++i) f.pair_ptr[i] = 0;
@@ -178,6 +178,23 @@ void analyse_fast(luna_uvu_plan* plan) {
   plan->m_ptr.push_back(static_cast<int>(plan->m_j.size()));
   f.m_total = total;
   if (total > kMaxMEntries) return;
+  // transposed program for the edge-attribute gradient: gy[j] = sum over (m, c) with that j of c * G[m]
+  {
+    std::vector<std::vector<std::pair<int, double>>> by_j(plan->Y);
+    for (int m = 0; m < total; ++m)
+      for (int t = plan->m_ptr[m]; t < plan->m_ptr[m + 1]; ++t) by_j[plan->m_j[t]].push_back({m, plan->m_c[t]});
+    plan->gy_ptr.clear();
+    plan->gy_m.clear();
+    plan->gy_c.clear();
+    for (int j = 0; j < plan->Y; ++j) {
+      plan->gy_ptr.push_back(static_cast<int>(plan->gy_m.size()));
+      for (auto [m, c] : by_j[j]) {
+        plan->gy_m.push_back(m);
+        plan->gy_c.push_back(c);
+      }
+    }
+    plan->gy_ptr.push_back(static_cast<int>(plan->gy_m.size()));
+  }
   plan->fast = f;
   plan->fast_ok = true;
 }
@@ -246,6 +263,18 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
     }
   }
   const size_t o_mc = append(mc.data(), mc.size());
+  const size_t o_gp = append(plan->gy_ptr.data(), plan->gy_ptr.size() * sizeof(int));
+  const size_t o_gm = append(plan->gy_m.data(), plan->gy_m.size() * sizeof(int));
+  std::vector<unsigned char> gc(plan->gy_c.size() * scalar);
+  for (size_t i = 0; i < plan->gy_c.size(); ++i) {
+    if (f64) {
+      std::memcpy(gc.data() + i * 8, &plan->gy_c[i], 8);
+    } else {
+      float v = static_cast<float>(plan->gy_c[i]);
+      std::memcpy(gc.data() + i * 4, &v, 4);
+    }
+  }
+  const size_t o_gc = append(gc.data(), gc.size());
 
   DeviceTables dt;
   dt.bytes = host.size();
@@ -274,6 +303,9 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   dt.m_ptr = reinterpret_cast<const int*>(base + o_mp);
   dt.m_j = reinterpret_cast<const int*>(base + o_mj);
   dt.m_c = base + o_mc;
+  dt.gy_ptr = reinterpret_cast<const int*>(base + o_gp);
+  dt.gy_m = reinterpret_cast<const int*>(base + o_gm);
+  dt.gy_c = base + o_gc;
   LUNA_CUDA_CHECK(cudaDeviceGetAttribute(&dt.sm_count, cudaDevAttrMultiProcessorCount, device));
   LUNA_CUDA_CHECK(cudaDeviceGetAttribute(&dt.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   auto inserted = plan->device_tables.emplace(device, dt);

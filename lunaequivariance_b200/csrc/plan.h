@@ -71,7 +71,7 @@ struct FastMeta {
   int o_off[kMaxFastL + 1];
   int xs_off[kMaxFastL + 1];  // offset of that block inside the staged x region (elements)
   int gs_off[kMaxFastL + 1];  // offset inside the staged g region
-  int pair_ptr[(kMaxFastL + 1) * (kMaxFastL + 1) + 1];  // paths sorted by (l1, l3)
+  int pair_ptr[(kMaxFastL + 1) * (kMaxFastL + 1) + 1];  // paths sorted by (l3, l1); index l3 * 4 + l1
   int w_soff[kMaxFastPaths];  // offset of a path's channel chunk inside the staged w region
   int w_goff[kMaxFastPaths];  // global weight offset of the path
   int m_off[kMaxFastPaths];   // offset of the path's d1 x d3 matrix in the per-edge M buffer
@@ -106,6 +106,9 @@ struct DeviceTables {
   const int* m_ptr = nullptr;
   const int* m_j = nullptr;
   const void* m_c = nullptr;
+  const int* gy_ptr = nullptr;  // [Y + 1] program of the edge-attribute gradient
+  const int* gy_m = nullptr;
+  const void* gy_c = nullptr;
   int sm_count = 0;
   int max_smem_optin = 0;
 };
@@ -133,6 +136,8 @@ struct luna_uvu_plan {
   luna::FastMeta fast{};
   std::vector<int> m_ptr, m_j;
   std::vector<double> m_c;
+  std::vector<int> gy_ptr, gy_m;
+  std::vector<double> gy_c;
 
   std::mutex mutex;
   std::map<int, luna::DeviceTables> device_tables;

@@ -1,4 +1,5 @@
 // Dispatch of the staged kernels by dtype and channels-per-lane, stage-count policy and shared-memory accounting.
+#include "uvu_fast_bwd.cuh"
 #include "uvu_fast_fwd.cuh"
 
 namespace luna {
@@ -32,6 +33,14 @@ extern template int launch_fast_fwd<float, 4>(const luna_uvu_plan*, const Device
 extern template int launch_fast_fwd<double, 1>(const luna_uvu_plan*, const DeviceTables&, const luna_graph*, const double*, const double*, const double*, double*, bool, cudaStream_t);
 extern template int launch_fast_fwd<double, 2>(const luna_uvu_plan*, const DeviceTables&, const luna_graph*, const double*, const double*, const double*, double*, bool, cudaStream_t);
 
+#define LUNA_BWD_SIG(T) const luna_uvu_plan*, const DeviceTables&, const luna_graph*, const T*, const T*, const T*, const T*, T*, bool, T*, bool, T*, bool, void*, int64_t, cudaStream_t
+extern template int launch_fast_bwd<float, 1>(LUNA_BWD_SIG(float));
+extern template int launch_fast_bwd<float, 2>(LUNA_BWD_SIG(float));
+extern template int launch_fast_bwd<float, 4>(LUNA_BWD_SIG(float));
+extern template int launch_fast_bwd<double, 1>(LUNA_BWD_SIG(double));
+extern template int launch_fast_bwd<double, 2>(LUNA_BWD_SIG(double));
+#undef LUNA_BWD_SIG
+
 }  // namespace fastk
 
 bool fast_available() { return true; }
@@ -44,14 +53,25 @@ int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which) {
   if (!plan->fast_ok) return 0;
   const FastMeta& f = plan->fast;
   const size_t elem = plan->dtype == LUNA_F64 ? 8 : 4;
-  const size_t fixed = static_cast<size_t>(f.m_total) * elem + 32 * elem + fastk::kMaxStages * sizeof(uint64_t);
-  const size_t stage = static_cast<size_t>(f.w_stage_elems + (which == 0 ? f.x_stage_elems : f.g_stage_elems)) * elem;
+  size_t fixed, stage;
+  if (which == 0) {
+    fixed = static_cast<size_t>(f.m_total) * elem + 32 * elem + fastk::kMaxStages * sizeof(uint64_t);
+    stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * elem;
+  } else {
+    fixed = plan->dtype == LUNA_F64 ? fastk::bwd_fixed_bytes<double>(f) : fastk::bwd_fixed_bytes<float>(f);
+    stage = static_cast<size_t>(f.w_stage_elems + f.g_stage_elems) * elem;
+  }
   size_t bytes = 0;
   fastk::choose_stages(stage, fixed, kSmemLimit, &bytes);
   return static_cast<int64_t>(bytes);
 }
 
-int64_t fast_scratch_bytes(const luna_uvu_plan*, int64_t, int64_t) { return 0; }
+// Per-chunk partial rows of gy when the channels of a block are split over several warps.
+int64_t fast_scratch_bytes(const luna_uvu_plan* plan, int64_t, int64_t num_edges) {
+  if (!plan->fast_ok || plan->force_generic || plan->fast.chunks <= 1) return 0;
+  const int64_t elem = plan->dtype == LUNA_F64 ? 8 : 4;
+  return static_cast<int64_t>(plan->fast.chunks) * num_edges * plan->Y * elem;
+}
 
 int fast_forward(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y, const void* w,
                  const void* rx, const void* ry, const void* rw, void* out, bool tangents, cudaStream_t stream) {
@@ -85,15 +105,29 @@ int fast_forward(luna_uvu_plan* plan, const luna_graph* graph, const void* x, co
   return LUNA_OK;
 }
 
-// Until the staged source-major kernel is linked, the first-order outputs come from the table-driven kernels.
 int fast_backward(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y, const void* w,
-                  const void* g, void* gx, bool acc_x, void* gy, bool acc_y, void* gw, bool acc_w, void*, int64_t,
-                  cudaStream_t stream) {
-  int rc = LUNA_OK;
-  if (gx && (rc = generic_contract(plan, graph, kFreeX, nullptr, y, w, g, gx, acc_x, stream)) != LUNA_OK) return rc;
-  if (gy && (rc = generic_contract(plan, graph, kFreeY, x, nullptr, w, g, gy, acc_y, stream)) != LUNA_OK) return rc;
-  if (gw && (rc = generic_contract(plan, graph, kFreeW, x, y, nullptr, g, gw, acc_w, stream)) != LUNA_OK) return rc;
-  return LUNA_OK;
+                  const void* g, void* gx, bool acc_x, void* gy, bool acc_y, void* gw, bool acc_w, void* scratch,
+                  int64_t scratch_bytes, cudaStream_t stream) {
+  const DeviceTables* dt = nullptr;
+  int rc = get_device_tables(plan, &dt);
+  if (rc != LUNA_OK) return rc;
+  const int cpl = plan->fast.cpl;
+  if (plan->dtype == LUNA_F64) {
+    auto X = static_cast<const double*>(x), Y = static_cast<const double*>(y), W = static_cast<const double*>(w);
+    auto G = static_cast<const double*>(g);
+    auto GX = static_cast<double*>(gx), GY = static_cast<double*>(gy), GW = static_cast<double*>(gw);
+    if (cpl == 2)
+      return fastk::launch_fast_bwd<double, 2>(plan, *dt, graph, X, Y, W, G, GX, acc_x, GY, acc_y, GW, acc_w, scratch, scratch_bytes, stream);
+    return fastk::launch_fast_bwd<double, 1>(plan, *dt, graph, X, Y, W, G, GX, acc_x, GY, acc_y, GW, acc_w, scratch, scratch_bytes, stream);
+  }
+  auto X = static_cast<const float*>(x), Y = static_cast<const float*>(y), W = static_cast<const float*>(w);
+  auto G = static_cast<const float*>(g);
+  auto GX = static_cast<float*>(gx), GY = static_cast<float*>(gy), GW = static_cast<float*>(gw);
+  if (cpl == 4)
+    return fastk::launch_fast_bwd<float, 4>(plan, *dt, graph, X, Y, W, G, GX, acc_x, GY, acc_y, GW, acc_w, scratch, scratch_bytes, stream);
+  if (cpl == 2)
+    return fastk::launch_fast_bwd<float, 2>(plan, *dt, graph, X, Y, W, G, GX, acc_x, GY, acc_y, GW, acc_w, scratch, scratch_bytes, stream);
+  return fastk::launch_fast_bwd<float, 1>(plan, *dt, graph, X, Y, W, G, GX, acc_x, GY, acc_y, GW, acc_w, scratch, scratch_bytes, stream);
 }
 
 }  // namespace luna

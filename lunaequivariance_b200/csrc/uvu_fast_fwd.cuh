@@ -133,8 +133,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
         static_for<0, LO + 1>([&](auto l3c) {
           constexpr int l3 = decltype(l3c)::value;
           constexpr int d3 = 2 * l3 + 1;
-          const int q_end = F.pair_ptr[l1 * (kMaxFastL + 1) + l3 + 1];
-          for (int q = F.pair_ptr[l1 * (kMaxFastL + 1) + l3]; q < q_end; ++q) {
+          const int q_end = F.pair_ptr[l3 * (kMaxFastL + 1) + l1 + 1];
+          for (int q = F.pair_ptr[l3 * (kMaxFastL + 1) + l1]; q < q_end; ++q) {
             T wv[CPL];
             load_vectors<T, CPL, 1>(ws + F.w_soff[q] + lane * CPL, wv);
             T mr[d1 * d3];

@@ -162,7 +162,7 @@ int launch(luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph,
   int64_t total = 0;
   switch (free_slot) {
     case kFreeG: total = N * tb.O; break;
-    case kFreeX: total = N * tb.X; break;
+    case kFreeX: total = (graph->num_src_nodes > 0 ? graph->num_src_nodes : N) * tb.X; break;
     case kFreeY: total = E * tb.Y; break;
     case kFreeW: total = E * tb.W; break;
     default: return fail(LUNA_ERR_INVALID_ARGUMENT, "unknown free slot %d", free_slot);

@@ -46,18 +46,25 @@ class LunaTPGraph:
     source_node_order: torch.Tensor | None = None
     node_tiers: torch.Tensor | None = None
     source_segments: SourceSegmentTables | None = None
+    # Rows of x / gx.  Equals num_nodes except on a destination-range shard of a partitioned graph, where the
+    # sources keep their global numbering (no counterpart in the reference, which is single-GPU).
+    num_src_nodes: int | None = None
     _tables: dict = field(default_factory=dict, init=False, repr=False, compare=False)
 
     @property
     def num_edges(self) -> int:
         return int(self.src.numel())
 
+    @property
+    def source_rows(self) -> int:
+        return self.num_nodes if self.num_src_nodes is None else int(self.num_src_nodes)
+
     def native(self) -> "_native.Graph":
         """The C-ABI view of this graph (cached; the tensors it points to are owned by the graph)."""
         view = self._tables.get("native")
         if view is None:
             view = _native.Graph(
-                self.num_nodes, self.num_edges, self.src.data_ptr(), self.dst.data_ptr(),
+                self.num_nodes, self.source_rows, self.num_edges, self.src.data_ptr(), self.dst.data_ptr(),
                 self.dst_rowptr.data_ptr(), self.src_rowptr.data_ptr(), self.edge_ids_by_src.data_ptr(),
             )
             self._tables["native"] = view
@@ -99,9 +106,8 @@ def _node_tiers(dst_rowptr, node_order, num_nodes, num_edges, device):
 
 def _bounds_host(src, dst):
     low = min(int(src.min()), int(dst.min()))
-    high = max(int(src.max()), int(dst.max()))
     unsorted = bool((dst[1:] < dst[:-1]).any()) if src.numel() > 1 else False
-    return low, high, unsorted
+    return low, int(src.max()), int(dst.max()), unsorted
 
 
 def _bounds_cuda(src, dst):
@@ -109,19 +115,22 @@ def _bounds_cuda(src, dst):
     edges = src.numel()
     scratch_bytes = lib.luna_graph_scratch_bytes(0, edges)
     scratch = torch.empty(max(scratch_bytes, 1), dtype=torch.uint8, device=src.device)
-    low, high, unsorted = ctypes.c_int64(0), ctypes.c_int64(-1), ctypes.c_int(0)
+    low, high_src, high_dst, unsorted = ctypes.c_int64(0), ctypes.c_int64(-1), ctypes.c_int64(-1), ctypes.c_int(0)
     bits = 64 if src.dtype == torch.int64 else 32
     _native.check(lib.luna_graph_bounds(src.data_ptr(), dst.data_ptr(), bits, edges, ctypes.byref(low),
-                                        ctypes.byref(high), ctypes.byref(unsorted), scratch.data_ptr(),
-                                        scratch_bytes, _native.current_stream(src.device)))
-    return low.value, high.value, bool(unsorted.value)
+                                        ctypes.byref(high_src), ctypes.byref(high_dst), ctypes.byref(unsorted),
+                                        scratch.data_ptr(), scratch_bytes, _native.current_stream(src.device)))
+    return low.value, high_src.value, high_dst.value, bool(unsorted.value)
 
 
-def make_graph(src: torch.Tensor, dst: torch.Tensor, num_nodes: int | None = None) -> LunaTPGraph:
+def make_graph(src: torch.Tensor, dst: torch.Tensor, num_nodes: int | None = None, *,
+               num_src_nodes: int | None = None) -> LunaTPGraph:
     """Build the topology tables from a destination-sorted edge list.
 
     ``src`` and ``dst`` are ``[edges]`` or ``[edges, 1]`` int32/int64 tensors on one device, ``dst`` ascending and
-    all edge data in the same order.  Build once per topology and reuse across layers.
+    all edge data in the same order.  Build once per topology and reuse across layers.  ``num_src_nodes`` (keyword
+    only, default ``num_nodes``) gives the row count of ``x`` when sources are numbered in a larger range than the
+    destinations, as on one shard of a partitioned graph.
     """
     if src.ndim == 2 and src.shape[1] == 1:
         src = src.squeeze(-1)
@@ -144,26 +153,30 @@ def make_graph(src: torch.Tensor, dst: torch.Tensor, num_nodes: int | None = Non
     required = 0
     if num_edges:
         with torch.cuda.device(device) if device.type == "cuda" else _NullContext():
-            low, high, unsorted = (_bounds_cuda if device.type == "cuda" else _bounds_host)(src, dst)
+            low, high_src, high_dst, unsorted = (_bounds_cuda if device.type == "cuda" else _bounds_host)(src, dst)
         if low < 0:
             raise ValueError("graph indices must be nonnegative.")
         if unsorted:
             raise ValueError("dst must be sorted in ascending order; src and edge data must follow the same order.")
-        required = high + 1
+        required = (high_dst if num_src_nodes is not None else max(high_src, high_dst)) + 1
+        if num_src_nodes is not None and num_src_nodes < high_src + 1:
+            raise ValueError(
+                f"num_src_nodes={num_src_nodes} must be at least {high_src + 1} for the supplied indices.")
     if num_nodes is None:
         num_nodes = required
     if num_nodes < required:
         raise ValueError(
             f"num_nodes={num_nodes} must be nonnegative and at least {required} for the supplied indices.")
-    if num_nodes >= (1 << 31):
+    source_rows = num_nodes if num_src_nodes is None else int(num_src_nodes)
+    if max(num_nodes, source_rows) >= (1 << 31):
         raise OverflowError("graph node count exceeds signed int32 capacity.")
     if max(num_edges, num_nodes + num_edges // SOURCE_SEGMENT_EDGES) >= (1 << 31) - 1024:
         raise OverflowError("graph edge count exceeds the int32 table capacity of this build.")
 
     if device.type == "cuda":
-        tables = _build_cuda(src, dst, num_nodes)
+        tables = _build_cuda(src, dst, num_nodes, source_rows)
     else:
-        tables = _build_host(src, dst, num_nodes)
+        tables = _build_host(src, dst, num_nodes, source_rows)
     src_out, dst_out, dst_rowptr, src_rowptr, edge_ids_by_src, node_order, source_node_order = tables
     graph = LunaTPGraph(
         src=src_out, dst=dst_out, num_nodes=num_nodes, dst_rowptr=dst_rowptr, src_rowptr=src_rowptr,
@@ -172,6 +185,7 @@ def make_graph(src: torch.Tensor, dst: torch.Tensor, num_nodes: int | None = Non
         node_order=node_order, source_node_order=source_node_order,
         node_tiers=_node_tiers(dst_rowptr, node_order, num_nodes, num_edges, device),
         source_segments=make_source_segments(src_rowptr),
+        num_src_nodes=None if num_src_nodes is None else source_rows,
     )
     return graph
 
@@ -184,17 +198,17 @@ class _NullContext:
         return False
 
 
-def _build_host(src, dst, num_nodes):
+def _build_host(src, dst, num_nodes, source_rows):
     device = src.device
 
-    def rowptr(index_tensor):
-        out = torch.zeros(num_nodes + 1, dtype=torch.int32, device=device)
+    def rowptr(index_tensor, rows):
+        out = torch.zeros(rows + 1, dtype=torch.int32, device=device)
         if index_tensor.numel():
-            counts = torch.bincount(index_tensor.long(), minlength=num_nodes)
+            counts = torch.bincount(index_tensor.long(), minlength=rows)
             out[1:] = torch.cumsum(counts, 0).to(torch.int32)
         return out
 
-    src_rowptr, dst_rowptr = rowptr(src), rowptr(dst)
+    src_rowptr, dst_rowptr = rowptr(src, source_rows), rowptr(dst, num_nodes)
     node_order = torch.argsort(dst_rowptr.diff().long(), descending=True, stable=True).to(torch.int32)
     source_node_order = torch.argsort(src_rowptr.diff().long(), descending=True, stable=True).to(torch.int32)
     edge_ids_by_src = torch.argsort(src.long(), stable=True).to(torch.int32)
@@ -202,20 +216,20 @@ def _build_host(src, dst, num_nodes):
             node_order, source_node_order)
 
 
-def _build_cuda(src, dst, num_nodes):
+def _build_cuda(src, dst, num_nodes, source_rows):
     lib = _native.library()
     device = src.device
     edges = src.numel()
     i32 = dict(dtype=torch.int32, device=device)
     out = [torch.empty(edges, **i32), torch.empty(edges, **i32), torch.empty(num_nodes + 1, **i32),
-           torch.empty(num_nodes + 1, **i32), torch.empty(edges, **i32), torch.empty(num_nodes, **i32),
-           torch.empty(num_nodes, **i32)]
+           torch.empty(source_rows + 1, **i32), torch.empty(edges, **i32), torch.empty(num_nodes, **i32),
+           torch.empty(source_rows, **i32)]
     with torch.cuda.device(device):
-        scratch_bytes = lib.luna_graph_scratch_bytes(num_nodes, edges)
+        scratch_bytes = lib.luna_graph_scratch_bytes(max(num_nodes, source_rows), edges)
         scratch = torch.empty(max(scratch_bytes, 1), dtype=torch.uint8, device=device)
         view = _native.GraphOut(*(t.data_ptr() for t in out))
         bits = 64 if src.dtype == torch.int64 else 32
-        _native.check(lib.luna_graph_build(src.data_ptr(), dst.data_ptr(), bits, num_nodes, edges,
+        _native.check(lib.luna_graph_build(src.data_ptr(), dst.data_ptr(), bits, num_nodes, source_rows, edges,
                                            ctypes.byref(view), scratch.data_ptr(), scratch_bytes,
                                            _native.current_stream(device)))
     return tuple(out)
