@@ -178,6 +178,18 @@ void analyse_fast(luna_uvu_plan* plan) {
   plan->m_ptr.push_back(static_cast<int>(plan->m_j.size()));
   f.m_total = total;
   if (total > kMaxMEntries) return;
+  // the same program in padded (ELL) form for the kernels: term t of entry m at [t * m_total + m]
+  f.m_terms = 1;
+  for (int m = 0; m < total; ++m) f.m_terms = std::max(f.m_terms, plan->m_ptr[m + 1] - plan->m_ptr[m]);
+  if (f.m_terms > 8) return;
+  plan->ell_c.assign(static_cast<size_t>(f.m_terms) * total, 0.0);
+  plan->ell_j.assign(static_cast<size_t>(f.m_terms) * total, 0);
+  for (int m = 0; m < total; ++m)
+    for (int t = plan->m_ptr[m]; t < plan->m_ptr[m + 1]; ++t) {
+      const size_t slot = static_cast<size_t>(t - plan->m_ptr[m]) * total + m;
+      plan->ell_c[slot] = plan->m_c[t];
+      plan->ell_j[slot] = static_cast<unsigned char>(plan->m_j[t]);
+    }
   // transposed program for the edge-attribute gradient: gy[j] = sum over (m, c) with that j of c * G[m]
   {
     std::vector<std::vector<std::pair<int, double>>> by_j(plan->Y);
@@ -251,14 +263,13 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   const size_t o_tk = append(tk.data(), tk.size());
   const size_t o_ti = append(ti.data(), ti.size());
   const size_t o_tj = append(tj.data(), tj.size());
-  const size_t o_mp = append(plan->m_ptr.data(), plan->m_ptr.size() * sizeof(int));
-  const size_t o_mj = append(plan->m_j.data(), plan->m_j.size() * sizeof(int));
-  std::vector<unsigned char> mc(plan->m_c.size() * scalar);
-  for (size_t i = 0; i < plan->m_c.size(); ++i) {
+  const size_t o_mj = append(plan->ell_j.data(), plan->ell_j.size());
+  std::vector<unsigned char> mc(plan->ell_c.size() * scalar);
+  for (size_t i = 0; i < plan->ell_c.size(); ++i) {
     if (f64) {
-      std::memcpy(mc.data() + i * 8, &plan->m_c[i], 8);
+      std::memcpy(mc.data() + i * 8, &plan->ell_c[i], 8);
     } else {
-      float v = static_cast<float>(plan->m_c[i]);
+      float v = static_cast<float>(plan->ell_c[i]);
       std::memcpy(mc.data() + i * 4, &v, 4);
     }
   }
@@ -300,9 +311,8 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   dt.terms_k = base + o_tk;
   dt.terms_i = base + o_ti;
   dt.terms_j = base + o_tj;
-  dt.m_ptr = reinterpret_cast<const int*>(base + o_mp);
-  dt.m_j = reinterpret_cast<const int*>(base + o_mj);
-  dt.m_c = base + o_mc;
+  dt.ell_j = base + o_mj;
+  dt.ell_c = base + o_mc;
   dt.gy_ptr = reinterpret_cast<const int*>(base + o_gp);
   dt.gy_m = reinterpret_cast<const int*>(base + o_gm);
   dt.gy_c = base + o_gc;

@@ -76,6 +76,7 @@ struct FastMeta {
   int w_goff[kMaxFastPaths];  // global weight offset of the path
   int m_off[kMaxFastPaths];   // offset of the path's d1 x d3 matrix in the per-edge M buffer
   int m_total;                // entries in the M buffer (padded)
+  int m_terms;                // terms per entry in the padded program (max over entries)
   int w_stage_elems, x_stage_elems, g_stage_elems;
   int n_w_pieces, n_x_pieces, n_g_pieces;
   CopyPiece pieces_w[kMaxFastPaths];
@@ -103,9 +104,8 @@ struct DeviceTables {
   const int* w_elem_path = nullptr;
   const int *rowptr_k = nullptr, *rowptr_i = nullptr, *rowptr_j = nullptr;
   const void *terms_k = nullptr, *terms_i = nullptr, *terms_j = nullptr;
-  const int* m_ptr = nullptr;
-  const int* m_j = nullptr;
-  const void* m_c = nullptr;
+  const unsigned char* ell_j = nullptr;  // [m_terms * m_total] y index of each term (padded form)
+  const void* ell_c = nullptr;           // [m_terms * m_total] coefficient of each term, 0 for padding
   const int* gy_ptr = nullptr;  // [Y + 1] program of the edge-attribute gradient
   const int* gy_m = nullptr;
   const void* gy_c = nullptr;
@@ -136,6 +136,8 @@ struct luna_uvu_plan {
   luna::FastMeta fast{};
   std::vector<int> m_ptr, m_j;
   std::vector<double> m_c;
+  std::vector<double> ell_c;
+  std::vector<unsigned char> ell_j;
   std::vector<int> gy_ptr, gy_m;
   std::vector<double> gy_c;
 

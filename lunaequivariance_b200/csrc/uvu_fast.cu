@@ -5,24 +5,32 @@
 namespace luna {
 namespace fastk {
 
-// Largest stage count in [2, 4] that still lets two CTAs share an SM; otherwise the largest that fits one CTA.
-int choose_stages(size_t stage_bytes, size_t fixed_bytes, int max_smem_optin, size_t* block_bytes) {
+// Warps per CTA and stages per warp.  Preference: 4 warps; the largest stage count in [2, 4] that still lets two
+// CTAs share an SM; otherwise one CTA per SM with 3 or 2 stages; otherwise fewer warps.  Returns 0 if even one warp
+// with two stages does not fit.
+int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
+                  size_t* block_bytes, int* warps) {
   const size_t two_per_sm = static_cast<size_t>(max_smem_optin) / 2 - 1024;
-  for (int stages = kMaxStages; stages >= 2; --stages) {
-    const size_t bytes = kWarps * (stages * stage_bytes + fixed_bytes);
-    if (bytes <= two_per_sm) {
-      *block_bytes = bytes;
-      return stages;
+  for (int w = kWarps; w >= 1; --w) {
+    for (int stages = kMaxStages; stages >= 2; --stages) {
+      const size_t bytes = shared_bytes + w * (stages * stage_bytes + fixed_bytes);
+      if (bytes <= two_per_sm) {
+        *block_bytes = bytes;
+        *warps = w;
+        return stages;
+      }
     }
-  }
-  for (int stages = 3; stages >= 2; --stages) {
-    const size_t bytes = kWarps * (stages * stage_bytes + fixed_bytes);
-    if (bytes <= static_cast<size_t>(max_smem_optin)) {
-      *block_bytes = bytes;
-      return stages;
+    for (int stages = 3; stages >= 2; --stages) {
+      const size_t bytes = shared_bytes + w * (stages * stage_bytes + fixed_bytes);
+      if (bytes <= static_cast<size_t>(max_smem_optin)) {
+        *block_bytes = bytes;
+        *warps = w;
+        return stages;
+      }
     }
   }
   *block_bytes = 0;
+  *warps = 0;
   return 0;
 }
 
@@ -62,7 +70,10 @@ int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which) {
     stage = static_cast<size_t>(f.w_stage_elems + f.g_stage_elems) * elem;
   }
   size_t bytes = 0;
-  fastk::choose_stages(stage, fixed, kSmemLimit, &bytes);
+  int warps = 0;
+  const size_t shared = plan->dtype == LUNA_F64 ? fastk::ell_bytes<double>(f.m_total, f.m_terms)
+                                                : fastk::ell_bytes<float>(f.m_total, f.m_terms);
+  fastk::choose_stages(stage, fixed, shared, kSmemLimit, &bytes, &warps);
   return static_cast<int64_t>(bytes);
 }
 

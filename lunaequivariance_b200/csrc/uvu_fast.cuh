@@ -162,14 +162,39 @@ __device__ __forceinline__ int64_t warp_lower_bound(const int* __restrict__ rowp
 }
 
 // ---- per-edge coupling matrices -------------------------------------------------------------------------------------
-// mbuf[m] = sum_t c[t] * ybuf[j[t]] over the CSR program; lanes stride over the entries.
+// The program that turns an edge's y row into the M matrices lives in shared memory in padded form: term t of
+// entry m is (ell_c[t * m_total + m], ell_j[t * m_total + m]); padding terms have coefficient 0.
 template <typename T>
-__device__ __forceinline__ void compute_m(const int* __restrict__ ptr, const int* __restrict__ jdx,
-                                          const T* __restrict__ coef, const T* ybuf, T* mbuf, int m_total, int lane) {
+__host__ __device__ inline size_t ell_bytes(int m_total, int m_terms) {
+  const size_t count = static_cast<size_t>(m_total) * m_terms;
+  return count * sizeof(T) + (count + 15) / 16 * 16;
+}
+
+// Copies the program from global to the start of the CTA's dynamic shared memory; all threads of the block call it.
+template <typename T>
+__device__ __forceinline__ void load_ell(unsigned char* smem, const T* __restrict__ gc,
+                                         const unsigned char* __restrict__ gj, int m_total, int m_terms,
+                                         const T** ell_c, const unsigned char** ell_j) {
+  const int count = m_total * m_terms;
+  T* c = reinterpret_cast<T*>(smem);
+  unsigned char* j = smem + static_cast<size_t>(count) * sizeof(T);
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    c[i] = gc[i];
+    j[i] = gj[i];
+  }
+  *ell_c = c;
+  *ell_j = j;
+  __syncthreads();
+}
+
+// mbuf[m] = sum_t c[t][m] * ybuf[j[t][m]]; lanes stride over the entries, conflict-free shared loads.
+template <typename T>
+__device__ __forceinline__ void compute_m(const T* ell_c, const unsigned char* ell_j, int m_terms, const T* ybuf,
+                                          T* mbuf, int m_total, int lane) {
+#pragma unroll 2
   for (int m = lane; m < m_total; m += 32) {
-    const int t0 = __ldg(ptr + m), t1 = __ldg(ptr + m + 1);
-    T a = T(0);
-    for (int t = t0; t < t1; ++t) a = fma(__ldg(coef + t), ybuf[__ldg(jdx + t)], a);
+    T a = ell_c[m] * ybuf[ell_j[m]];
+    for (int t = 1; t < m_terms; ++t) a = fma(ell_c[t * m_total + m], ybuf[ell_j[t * m_total + m]], a);
     mbuf[m] = a;
   }
 }

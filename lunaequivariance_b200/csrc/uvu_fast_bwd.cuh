@@ -36,9 +36,8 @@ struct BwdParams {
   const int* dst;
   const int* src_rowptr;
   const int* edge_ids;
-  const int* m_ptr;
-  const int* m_j;
-  const T* m_c;
+  const unsigned char* ell_j;
+  const T* ell_c;
   const int* gy_ptr;
   const int* gy_m;
   const T* gy_c;
@@ -85,7 +84,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) fast_bwd_kernel(const __grid_c
   const int stages = P.stages;
   const int stage_elems = F.w_stage_elems + F.g_stage_elems;
   const size_t warp_bytes = static_cast<size_t>(stages) * stage_elems * sizeof(T) + bwd_fixed_bytes<T>(F);
-  unsigned char* base = smem_raw + static_cast<size_t>(warp) * warp_bytes;
+  const T* ell_c;
+  const unsigned char* ell_j;
+  load_ell<T>(smem_raw, P.ell_c, P.ell_j, F.m_total, F.m_terms, &ell_c, &ell_j);
+  unsigned char* base = smem_raw + ell_bytes<T>(F.m_total, F.m_terms) + static_cast<size_t>(warp) * warp_bytes;
   T* stage_mem = reinterpret_cast<T*>(base);
   T* mbuf = stage_mem + static_cast<size_t>(stages) * stage_elems;
   T* gbuf = mbuf + F.m_total;
@@ -102,8 +104,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) fast_bwd_kernel(const __grid_c
   const int chw = 32 * CPL;
   const int c0 = blockIdx.y * chw;
   const int64_t E = P.num_edges, N = P.num_src_nodes;
-  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kWarps;
-  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  const int nwarps = blockDim.x >> 5;
+  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * nwarps;
+  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * nwarps + warp;
   const int64_t bound_lo = E * gwarp / total_warps, bound_hi = E * (gwarp + 1) / total_warps;
   const int64_t n_lo = warp_lower_bound(P.src_rowptr, N, bound_lo, lane);
   const int64_t n_hi = gwarp == total_warps - 1 ? N : warp_lower_bound(P.src_rowptr, N, bound_hi, lane);
@@ -113,12 +116,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) fast_bwd_kernel(const __grid_c
 
   const uint32_t stage_bytes = static_cast<uint32_t>(stage_elems * sizeof(T));
   const int n_pieces = F.n_w_pieces + F.n_g_pieces;
-  auto issue = [&](int64_t pos, int s) {
+  auto issue = [&](int64_t e, int64_t d_node, int s) {
     uint64_t* bar = &bars[s];
     if (lane == 0) mbar_arrive_expect_tx(bar, stage_bytes);
     __syncwarp();
     T* dstm = stage_mem + static_cast<size_t>(s) * stage_elems;
-    const int64_t e = P.edge_ids[pos];
     for (int pi = lane; pi < n_pieces; pi += 32) {
       if (pi < F.n_w_pieces) {
         const CopyPiece pc = F.pieces_w[pi];
@@ -126,14 +128,21 @@ __global__ void __launch_bounds__(kWarps * 32, 1) fast_bwd_kernel(const __grid_c
                       static_cast<uint32_t>(pc.n * sizeof(T)), bar);
       } else {
         const CopyPiece pc = F.pieces_g[pi - F.n_w_pieces];
-        const int64_t d_node = P.dst[e];
         bulk_copy_g2s(dstm + F.w_stage_elems + pc.s_off, P.g + d_node * F.O + pc.g_off + c0 * pc.comp,
                       static_cast<uint32_t>(pc.n * sizeof(T)), bar);
       }
     }
   };
   for (int s = 0; s < stages; ++s)
-    if (p_begin + s < p_end) issue(p_begin + s, s);
+    if (p_begin + s < p_end) {
+      const int e0 = P.edge_ids[p_begin + s];
+      issue(e0, P.dst[e0], s);
+    }
+  // (edge id, destination) of the edges issued in the next two iterations, fetched early: the two loads depend on
+  // each other, so the id runs two iterations ahead and the destination one
+  int id_a1 = p_begin + stages < p_end ? P.edge_ids[p_begin + stages] : 0;
+  int dst_a1 = p_begin + stages < p_end ? P.dst[id_a1] : 0;
+  int id_a2 = p_begin + stages + 1 < p_end ? P.edge_ids[p_begin + stages + 1] : 0;
 
   int64_t e_next = p_begin < p_end ? P.edge_ids[p_begin] : 0;
   T y_next = (lane < F.Y && p_begin < p_end) ? P.y[e_next * F.Y + lane] : T(0);
@@ -167,7 +176,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) fast_bwd_kernel(const __grid_c
       const T* gs = ws + F.w_stage_elems;
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
-      compute_m<T>(P.m_ptr, P.m_j, P.m_c, ybuf, mbuf, F.m_total, lane);
+      compute_m<T>(ell_c, ell_j, F.m_terms, ybuf, mbuf, F.m_total, lane);
       if (pos + 1 < p_end && lane < F.Y) y_next = P.y[e_next * F.Y + lane];
       __syncwarp();
 
@@ -271,7 +280,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) fast_bwd_kernel(const __grid_c
         }
       }
       __syncwarp();
-      if (pos + stages < p_end) issue(pos + stages, s);
+      const int id_now = id_a1, dst_now = dst_a1;
+      id_a1 = id_a2;
+      if (pos + stages + 1 < p_end) dst_a1 = P.dst[id_a1];
+      if (pos + stages + 2 < p_end) id_a2 = P.edge_ids[pos + stages + 2];
+      if (pos + stages < p_end) issue(id_now, dst_now, s);
     }
     if (!alive) break;
     if (want_x) {
@@ -309,7 +322,8 @@ __global__ void reduce_gy_partial(const T* __restrict__ partial, T* __restrict__
   gy[idx] = acc;
 }
 
-int choose_stages(size_t stage_bytes, size_t fixed_bytes, int max_smem_optin, size_t* block_bytes);
+int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
+                  size_t* block_bytes, int* warps);
 
 template <typename T, int CPL, int LX, int LO>
 int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
@@ -329,9 +343,8 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.dst = graph->dst;
   P.src_rowptr = graph->src_rowptr;
   P.edge_ids = graph->edge_ids_by_src;
-  P.m_ptr = dt.m_ptr;
-  P.m_j = dt.m_j;
-  P.m_c = static_cast<const T*>(dt.m_c);
+  P.ell_j = dt.ell_j;
+  P.ell_c = static_cast<const T*>(dt.ell_c);
   P.gy_ptr = dt.gy_ptr;
   P.gy_m = dt.gy_m;
   P.gy_c = static_cast<const T*>(dt.gy_c);
@@ -352,16 +365,17 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   }
   const size_t stage = static_cast<size_t>(f.w_stage_elems + f.g_stage_elems) * sizeof(T);
   size_t block_bytes = 0;
-  P.stages = choose_stages(stage, bwd_fixed_bytes<T>(f), dt.max_smem_optin, &block_bytes);
+  int nwarps = kWarps;
+  P.stages = choose_stages(stage, bwd_fixed_bytes<T>(f), ell_bytes<T>(f.m_total, f.m_terms), dt.max_smem_optin, &block_bytes, &nwarps);
   if (P.stages == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
   auto kernel = fast_bwd_kernel<T, CPL, LX, LO>;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
   int64_t warps = std::max<int64_t>(1, ceil_div(graph->num_edges, 256));
-  int64_t blocks = ceil_div(warps, kWarps);
+  int64_t blocks = ceil_div(warps, nwarps);
   const int64_t wave = static_cast<int64_t>(dt.sm_count) * std::max<int64_t>(1, dt.max_smem_optin / std::max<size_t>(block_bytes, 1));
   if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
-  kernel<<<grid, kWarps * 32, block_bytes, stream>>>(P);
+  kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged backward");
   if (P.gy_partial != nullptr) {
     const unsigned rb = static_cast<unsigned>(ceil_div(partial_count, 256));

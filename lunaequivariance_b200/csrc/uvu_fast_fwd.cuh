@@ -23,9 +23,8 @@ struct FwdParams {
   T* out;
   const int* src;
   const int* dst_rowptr;
-  const int* m_ptr;
-  const int* m_j;
-  const T* m_c;
+  const unsigned char* ell_j;
+  const T* ell_c;
   int* status;
   int64_t num_nodes, num_edges;
   int stages;
@@ -45,7 +44,10 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int stages = P.stages;
   const int stage_elems = F.w_stage_elems + F.x_stage_elems;
-  unsigned char* base = smem_raw + static_cast<size_t>(warp) * fwd_warp_bytes<T>(F, stages);
+  const T* ell_c;
+  const unsigned char* ell_j;
+  load_ell<T>(smem_raw, P.ell_c, P.ell_j, F.m_total, F.m_terms, &ell_c, &ell_j);
+  unsigned char* base = smem_raw + ell_bytes<T>(F.m_total, F.m_terms) + static_cast<size_t>(warp) * fwd_warp_bytes<T>(F, stages);
   T* stage_mem = reinterpret_cast<T*>(base);
   T* mbuf = stage_mem + static_cast<size_t>(stages) * stage_elems;
   T* ybuf = mbuf + F.m_total;
@@ -60,8 +62,9 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
   const int chw = 32 * CPL;
   const int c0 = blockIdx.y * chw;  // first channel of this warp's chunk
   const int64_t E = P.num_edges, N = P.num_nodes;
-  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kWarps;
-  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  const int nwarps = blockDim.x >> 5;
+  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * nwarps;
+  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * nwarps + warp;
   const int64_t bound_lo = E * gwarp / total_warps, bound_hi = E * (gwarp + 1) / total_warps;
   const int64_t n_lo = warp_lower_bound(P.dst_rowptr, N, bound_lo, lane);
   const int64_t n_hi = gwarp == total_warps - 1 ? N : warp_lower_bound(P.dst_rowptr, N, bound_hi, lane);
@@ -70,7 +73,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
 
   const uint32_t stage_bytes = static_cast<uint32_t>(stage_elems * sizeof(T));
   const int n_pieces = F.n_w_pieces + F.n_x_pieces;
-  auto issue = [&](int64_t e, int s) {
+  auto issue = [&](int64_t e, int64_t s_node, int s) {
     uint64_t* bar = &bars[s];
     if (lane == 0) mbar_arrive_expect_tx(bar, stage_bytes);
     __syncwarp();
@@ -82,7 +85,6 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
                       static_cast<uint32_t>(pc.n * sizeof(T)), bar);
       } else {
         const CopyPiece pc = F.pieces_x[pi - F.n_w_pieces];
-        const int64_t s_node = P.src[e];
         bulk_copy_g2s(dst + F.w_stage_elems + pc.s_off, P.x + s_node * F.X + pc.g_off + c0 * pc.comp,
                       static_cast<uint32_t>(pc.n * sizeof(T)), bar);
       }
@@ -90,7 +92,9 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
   };
 
   for (int s = 0; s < stages; ++s)
-    if (e_begin + s < e_end) issue(e_begin + s, s);
+    if (e_begin + s < e_end) issue(e_begin + s, P.src[e_begin + s], s);
+  // source node of the edge that will be issued in the next iteration, fetched one iteration early
+  int src_ahead = e_begin + stages < e_end ? P.src[e_begin + stages] : 0;
 
   T y_next = (lane < F.Y && e_begin < e_end) ? P.y[e_begin * F.Y + lane] : T(0);
   constexpr int XR = (LX + 1) * (LX + 1) * CPL;
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
       // coupling matrices of this edge
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
-      compute_m<T>(P.m_ptr, P.m_j, P.m_c, ybuf, mbuf, F.m_total, lane);
+      compute_m<T>(ell_c, ell_j, F.m_terms, ybuf, mbuf, F.m_total, lane);
       if (e + 1 < e_end && lane < F.Y) y_next = P.y[(e + 1) * F.Y + lane];
       __syncwarp();
       // this lane's channels of the gathered x row
@@ -155,7 +159,9 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
         });
       });
       __syncwarp();  // every lane is done with this stage, mbuf and ybuf
-      if (e + stages < e_end) issue(e + stages, s);
+      const int src_now = src_ahead;
+      if (e + stages + 1 < e_end) src_ahead = P.src[e + stages + 1];
+      if (e + stages < e_end) issue(e + stages, src_now, s);
     }
     if (!alive) break;
     // flush the node's accumulators
@@ -183,7 +189,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
 }
 
 // Host side: picks the stage count, sets the shared-memory attribute, launches.
-int choose_stages(size_t stage_bytes, size_t fixed_bytes, int max_smem_optin, size_t* block_bytes);
+int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
+                  size_t* block_bytes, int* warps);
 
 template <typename T, int CPL, int LX, int LO>
 int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
@@ -197,9 +204,8 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.out = out;
   P.src = graph->src;
   P.dst_rowptr = graph->dst_rowptr;
-  P.m_ptr = dt.m_ptr;
-  P.m_j = dt.m_j;
-  P.m_c = static_cast<const T*>(dt.m_c);
+  P.ell_j = dt.ell_j;
+  P.ell_c = static_cast<const T*>(dt.ell_c);
   P.status = dt.status;
   P.num_nodes = graph->num_nodes;
   P.num_edges = graph->num_edges;
@@ -207,17 +213,18 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
   const size_t fixed = static_cast<size_t>(f.m_total) * sizeof(T) + 32 * sizeof(T) + kMaxStages * sizeof(uint64_t);
   size_t block_bytes = 0;
-  P.stages = choose_stages(stage, fixed, dt.max_smem_optin, &block_bytes);
+  int nwarps = kWarps;
+  P.stages = choose_stages(stage, fixed, ell_bytes<T>(f.m_total, f.m_terms), dt.max_smem_optin, &block_bytes, &nwarps);
   if (P.stages == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged forward needs more shared memory than the device has");
   auto kernel = fast_fwd_kernel<T, CPL, LX, LO>;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
   // about 512 edges per warp, rounded to whole waves of two CTAs per SM
   int64_t warps = std::max<int64_t>(1, ceil_div(graph->num_edges, 512));
-  int64_t blocks = ceil_div(warps, kWarps);
-  const int64_t wave = static_cast<int64_t>(dt.sm_count) * 2;
+  int64_t blocks = ceil_div(warps, nwarps);
+  const int64_t wave = static_cast<int64_t>(dt.sm_count) * std::max<int64_t>(1, dt.max_smem_optin / std::max<size_t>(block_bytes, 1));
   if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
-  kernel<<<grid, kWarps * 32, block_bytes, stream>>>(P);
+  kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged forward");
   return LUNA_OK;
 }
