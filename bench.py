@@ -33,6 +33,7 @@ WORKLOADS = {
     "cfg5": ("64x0e+64x1o+64x2e", 2, "64x0e+64x1o+64x2e", torch.float32, 250_000, "radius"),
     "cfg4": ("64x0e+64x1o+64x2e+64x3o", 3, "64x0e+64x1o+64x2e+64x3o", torch.float32, 100_000, "degree40"),
     "cfg1": ("32x1o", 1, "32x0e", torch.float64, 1_000, "degree16"),
+    "lmax1": ("128x0e+128x1o", 1, "128x0e+128x1o", torch.float32, 100_000, "radius"),
 }
 DENSITY, CUTOFF = 0.1, 5.0
 

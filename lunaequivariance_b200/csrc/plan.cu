@@ -3,6 +3,7 @@
 #include "plan.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -81,6 +82,10 @@ void analyse_fast(luna_uvu_plan* plan) {
     f.cpl = ch % 128 == 0 ? 4 : (ch % 64 == 0 ? 2 : 1);
   else
     f.cpl = ch % 64 == 0 ? 2 : 1;
+  if (const char* knob = std::getenv("LUNA_B200_CPL")) {  // tuning knob: cap the channels per lane
+    const int cap = std::atoi(knob);
+    while (cap >= 1 && f.cpl > cap) f.cpl /= 2;
+  }
   const int chw = 32 * f.cpl;
   f.chunks = ch / chw;
   f.ch = ch;

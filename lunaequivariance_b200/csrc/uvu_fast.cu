@@ -1,31 +1,29 @@
 // Dispatch of the staged kernels by dtype and channels-per-lane, stage-count policy and shared-memory accounting.
+#include <cstdlib>
+
 #include "uvu_fast_bwd.cuh"
 #include "uvu_fast_fwd.cuh"
 
 namespace luna {
 namespace fastk {
 
-// Warps per CTA and stages per warp.  Preference: 4 warps; the largest stage count in [2, 4] that still lets two
-// CTAs share an SM; otherwise one CTA per SM with 3 or 2 stages; otherwise fewer warps.  Returns 0 if even one warp
-// with two stages does not fit.
+// Warps per CTA and stages per warp.  The kernels hide per-edge latency with resident warps, so the policy
+// maximises CTAs per SM first (up to 4 CTAs of 4 warps), then stages (3 preferred over 2); if one CTA of 4 warps
+// with two stages does not fit, the CTA shrinks.  Returns 0 if even one warp with two stages does not fit.
 int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
                   size_t* block_bytes, int* warps) {
-  const size_t two_per_sm = static_cast<size_t>(max_smem_optin) / 2 - 1024;
+  int max_ctas = 4;
+  if (const char* knob = std::getenv("LUNA_B200_MAX_CTAS")) max_ctas = std::max(1, std::atoi(knob));
   for (int w = kWarps; w >= 1; --w) {
-    for (int stages = kMaxStages; stages >= 2; --stages) {
-      const size_t bytes = shared_bytes + w * (stages * stage_bytes + fixed_bytes);
-      if (bytes <= two_per_sm) {
-        *block_bytes = bytes;
-        *warps = w;
-        return stages;
-      }
-    }
-    for (int stages = 3; stages >= 2; --stages) {
-      const size_t bytes = shared_bytes + w * (stages * stage_bytes + fixed_bytes);
-      if (bytes <= static_cast<size_t>(max_smem_optin)) {
-        *block_bytes = bytes;
-        *warps = w;
-        return stages;
+    for (int ctas = max_ctas; ctas >= 1; --ctas) {
+      const size_t budget = static_cast<size_t>(max_smem_optin + 1024) / ctas - 1024;  // 1 KB reserved per CTA
+      for (int stages = 3; stages >= 2; --stages) {
+        const size_t bytes = shared_bytes + w * (stages * stage_bytes + fixed_bytes);
+        if (bytes <= budget) {
+          *block_bytes = bytes;
+          *warps = w;
+          return stages;
+        }
       }
     }
   }
