@@ -45,48 +45,15 @@ void build_slots(const std::vector<PathRec>& paths, Key key, std::vector<SlotRec
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-// Decide whether the staged kernels apply and fill plan->fast.
-void analyse_fast(luna_uvu_plan* plan) {
-  plan->fast_ok = false;
+// Fills the stage layout, path order and M program of `f` for `cpl` channels per lane and `sub` warps sharing one
+// staged chunk of 32 * cpl * sub channels.  Returns false if a limit of the staged kernels is exceeded.
+bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl, int sub, bool build_programs) {
   const auto& paths = plan->paths;
-  if (paths.empty() || paths.size() > kMaxFastPaths) return;
-  const int elem = plan->dtype == LUNA_F64 ? 8 : 4;
-  const int align = 16 / elem;  // elements per 16 bytes
   const int ch = paths[0].ch;
-  if (ch % 32 != 0) return;
-  if (plan->Y > 32) return;
-  FastMeta f{};
-  f.LX = f.LO = 0;
-  for (int l = 0; l <= kMaxFastL; ++l) f.x_off[l] = f.o_off[l] = f.xs_off[l] = f.gs_off[l] = -1;
-  for (const auto& p : paths) {
-    if (p.ch != ch || p.w_stride != 1) return;
-    const int l1 = (p.d1 - 1) / 2, l3 = (p.d3 - 1) / 2;
-    if (l1 > kMaxFastL || l3 > kMaxFastL) return;
-    if (f.x_off[l1] >= 0 && f.x_off[l1] != p.x_off) return;  // two x blocks of the same degree
-    if (f.o_off[l3] >= 0 && f.o_off[l3] != p.out_off) return;
-    f.x_off[l1] = p.x_off;
-    f.o_off[l3] = p.out_off;
-    f.LX = std::max(f.LX, l1);
-    f.LO = std::max(f.LO, l3);
-    if (p.w_off % align || p.x_off % align || p.out_off % align) return;
-  }
-  // a block offset must not be shared by two different degrees
-  for (int a = 0; a <= kMaxFastL; ++a)
-    for (int b = a + 1; b <= kMaxFastL; ++b) {
-      if (f.x_off[a] >= 0 && f.x_off[a] == f.x_off[b]) return;
-      if (f.o_off[a] >= 0 && f.o_off[a] == f.o_off[b]) return;
-    }
-  if (plan->X % align || plan->O % align || plan->W % align) return;
-
-  if (plan->dtype == LUNA_F32)
-    f.cpl = ch % 128 == 0 ? 4 : (ch % 64 == 0 ? 2 : 1);
-  else
-    f.cpl = ch % 64 == 0 ? 2 : 1;
-  if (const char* knob = std::getenv("LUNA_B200_CPL")) {  // tuning knob: cap the channels per lane
-    const int cap = std::atoi(knob);
-    while (cap >= 1 && f.cpl > cap) f.cpl /= 2;
-  }
-  const int chw = 32 * f.cpl;
+  f.cpl = cpl;
+  f.sub = sub;
+  const int chw = 32 * cpl * sub;
+  if (ch % chw != 0) return false;
   f.chunks = ch / chw;
   f.ch = ch;
   f.X = plan->X;
@@ -154,14 +121,15 @@ void analyse_fast(luna_uvu_plan* plan) {
   layout_blocks(f.x_off, f.xs_off, f.pieces_x, f.n_x_pieces, f.x_stage_elems, f.LX);
   layout_blocks(f.o_off, f.gs_off, f.pieces_g, f.n_g_pieces, f.g_stage_elems, f.LO);
 
-  // per-edge M buffer and the program that fills it
-  plan->m_ptr.clear();
-  plan->m_j.clear();
-  plan->m_c.clear();
+  // per-edge M buffer (path matrices back to back, each padded to a multiple of 4 entries)
+  std::vector<int> m_ptr, m_j;
+  std::vector<double> m_c;
   int total = 0;
+  std::vector<double> l3_cost(kMaxFastL + 1, 0.0);
   for (size_t q = 0; q < order.size(); ++q) {
     const PathRec& p = paths[order[q]];
     f.m_off[q] = total;
+    l3_cost[(p.d3 - 1) / 2] += p.d1 * p.d3 + p.d3 + 4;
     // terms sorted by k give (i, j) per k; rebuild a dense (i,k) -> list of (j, c)
     std::vector<std::vector<std::pair<int, double>>> cell(p.d1 * p.d3);
     for (int k = 0; k < p.d3; ++k)
@@ -171,48 +139,120 @@ void analyse_fast(luna_uvu_plan* plan) {
       }
     const int padded = round_up(p.d1 * p.d3, 4);
     for (int m = 0; m < padded; ++m) {
-      plan->m_ptr.push_back(static_cast<int>(plan->m_j.size()));
+      m_ptr.push_back(static_cast<int>(m_j.size()));
       if (m < p.d1 * p.d3)
         for (auto [j, c] : cell[m]) {
-          plan->m_j.push_back(j);
-          plan->m_c.push_back(c);
+          m_j.push_back(j);
+          m_c.push_back(c);
         }
     }
     total += padded;
   }
-  plan->m_ptr.push_back(static_cast<int>(plan->m_j.size()));
+  m_ptr.push_back(static_cast<int>(m_j.size()));
   f.m_total = total;
-  if (total > kMaxMEntries) return;
+  if (total > kMaxMEntries) return false;
+
+  // roles of the forward kernel: output degrees spread over at most three warps by cost, heaviest first
+  {
+    std::vector<int> present;
+    for (int l = 0; l <= kMaxFastL; ++l) {
+      f.role_of_l3[l] = 0;
+      if (f.o_off[l] >= 0) present.push_back(l);
+    }
+    std::sort(present.begin(), present.end(), [&](int a, int b) { return l3_cost[a] > l3_cost[b]; });
+    f.nroles = std::min<int>(3, static_cast<int>(present.size()));
+    std::vector<double> load(f.nroles, 0.0);
+    for (int l : present) {
+      const int r = static_cast<int>(std::min_element(load.begin(), load.end()) - load.begin());
+      f.role_of_l3[l] = r;
+      load[r] += l3_cost[l];
+    }
+  }
+  if (!build_programs) return true;
+
   // the same program in padded (ELL) form for the kernels: term t of entry m at [t * m_total + m]
-  f.m_terms = 1;
-  for (int m = 0; m < total; ++m) f.m_terms = std::max(f.m_terms, plan->m_ptr[m + 1] - plan->m_ptr[m]);
-  if (f.m_terms > 8) return;
+  f.m_terms = 2;  // at least two (zero-padded) terms so that the kernels can read two unconditionally
+  for (int m = 0; m < total; ++m) f.m_terms = std::max(f.m_terms, m_ptr[m + 1] - m_ptr[m]);
+  if (f.m_terms > 2) return false;  // the staged kernels read exactly two terms per entry (enough for l <= 3)
   plan->ell_c.assign(static_cast<size_t>(f.m_terms) * total, 0.0);
   plan->ell_j.assign(static_cast<size_t>(f.m_terms) * total, 0);
   for (int m = 0; m < total; ++m)
-    for (int t = plan->m_ptr[m]; t < plan->m_ptr[m + 1]; ++t) {
-      const size_t slot = static_cast<size_t>(t - plan->m_ptr[m]) * total + m;
-      plan->ell_c[slot] = plan->m_c[t];
-      plan->ell_j[slot] = static_cast<unsigned char>(plan->m_j[t]);
+    for (int t = m_ptr[m]; t < m_ptr[m + 1]; ++t) {
+      const size_t slot = static_cast<size_t>(t - m_ptr[m]) * total + m;
+      plan->ell_c[slot] = m_c[t];
+      plan->ell_j[slot] = static_cast<unsigned char>(m_j[t]);
     }
   // transposed program for the edge-attribute gradient: gy[j] = sum over (m, c) with that j of c * G[m]
-  {
-    std::vector<std::vector<std::pair<int, double>>> by_j(plan->Y);
-    for (int m = 0; m < total; ++m)
-      for (int t = plan->m_ptr[m]; t < plan->m_ptr[m + 1]; ++t) by_j[plan->m_j[t]].push_back({m, plan->m_c[t]});
-    plan->gy_ptr.clear();
-    plan->gy_m.clear();
-    plan->gy_c.clear();
-    for (int j = 0; j < plan->Y; ++j) {
-      plan->gy_ptr.push_back(static_cast<int>(plan->gy_m.size()));
-      for (auto [m, c] : by_j[j]) {
-        plan->gy_m.push_back(m);
-        plan->gy_c.push_back(c);
-      }
-    }
+  std::vector<std::vector<std::pair<int, double>>> by_j(plan->Y);
+  for (int m = 0; m < total; ++m)
+    for (int t = m_ptr[m]; t < m_ptr[m + 1]; ++t) by_j[m_j[t]].push_back({m, m_c[t]});
+  plan->gy_ptr.clear();
+  plan->gy_m.clear();
+  plan->gy_c.clear();
+  for (int j = 0; j < plan->Y; ++j) {
     plan->gy_ptr.push_back(static_cast<int>(plan->gy_m.size()));
+    for (auto [m, c] : by_j[j]) {
+      plan->gy_m.push_back(m);
+      plan->gy_c.push_back(c);
+    }
   }
-  plan->fast = f;
+  plan->gy_ptr.push_back(static_cast<int>(plan->gy_m.size()));
+  return true;
+}
+
+// Decide whether the staged kernels apply and fill plan->fast (per-warp stages, used by the source-major kernel)
+// and plan->fastc (one stage ring per CTA shared by role warps, used by the destination-major kernel).
+void analyse_fast(luna_uvu_plan* plan) {
+  plan->fast_ok = false;
+  const auto& paths = plan->paths;
+  if (paths.empty() || paths.size() > kMaxFastPaths) return;
+  const int elem = plan->dtype == LUNA_F64 ? 8 : 4;
+  const int align = 16 / elem;  // elements per 16 bytes
+  const int ch = paths[0].ch;
+  if (ch % 32 != 0) return;
+  if (plan->Y > 32) return;
+  FastMeta f{};
+  f.LX = f.LO = 0;
+  for (int l = 0; l <= kMaxFastL; ++l) f.x_off[l] = f.o_off[l] = f.xs_off[l] = f.gs_off[l] = -1;
+  for (const auto& p : paths) {
+    if (p.ch != ch || p.w_stride != 1) return;
+    const int l1 = (p.d1 - 1) / 2, l3 = (p.d3 - 1) / 2;
+    if (l1 > kMaxFastL || l3 > kMaxFastL) return;
+    if (f.x_off[l1] >= 0 && f.x_off[l1] != p.x_off) return;  // two x blocks of the same degree
+    if (f.o_off[l3] >= 0 && f.o_off[l3] != p.out_off) return;
+    f.x_off[l1] = p.x_off;
+    f.o_off[l3] = p.out_off;
+    f.LX = std::max(f.LX, l1);
+    f.LO = std::max(f.LO, l3);
+    if (p.w_off % align || p.x_off % align || p.out_off % align) return;
+  }
+  // a block offset must not be shared by two different degrees
+  for (int a = 0; a <= kMaxFastL; ++a)
+    for (int b = a + 1; b <= kMaxFastL; ++b) {
+      if (f.x_off[a] >= 0 && f.x_off[a] == f.x_off[b]) return;
+      if (f.o_off[a] >= 0 && f.o_off[a] == f.o_off[b]) return;
+    }
+  if (plan->X % align || plan->O % align || plan->W % align) return;
+
+  int cpl;
+  if (plan->dtype == LUNA_F32)
+    cpl = ch % 128 == 0 ? 4 : (ch % 64 == 0 ? 2 : 1);
+  else
+    cpl = ch % 64 == 0 ? 2 : 1;
+  if (const char* knob = std::getenv("LUNA_B200_CPL")) {  // tuning knob: cap the channels per lane
+    const int cap = std::atoi(knob);
+    while (cap >= 1 && cpl > cap) cpl /= 2;
+  }
+  FastMeta per_warp = f, per_cta = f;
+  if (!fill_layout(plan, per_warp, cpl, 1, true)) return;
+  // CTA layout: at most two channels per lane (small code), two warps side by side when the block is wide enough
+  const int cpl_c = std::min(cpl, 2);
+  int sub = ch % (32 * cpl_c * 2) == 0 ? 2 : 1;
+  if (const char* knob = std::getenv("LUNA_B200_SUB")) sub = std::max(1, std::atoi(knob));
+  if (!fill_layout(plan, per_cta, cpl_c, sub, false)) return;
+  per_cta.m_terms = per_warp.m_terms;
+  plan->fast = per_warp;
+  plan->fastc = per_cta;
   plan->fast_ok = true;
 }
 

@@ -50,7 +50,7 @@ struct GenericTables {
 constexpr int kMaxFastPaths = 64;
 constexpr int kMaxFastL = 3;          // degrees 0..3 on x and out
 constexpr int kMaxPieces = 80;        // bulk-copy pieces per edge stage
-constexpr int kMaxMEntries = 2048;
+constexpr int kMaxMEntries = 512;     // per-edge M buffer entries (two warps x 8 entries per lane)
 
 struct CopyPiece {
   int g_off;   // element offset inside the global row for channel chunk 0
@@ -63,6 +63,9 @@ struct CopyPiece {
 struct FastMeta {
   int LX, LO;                 // highest degree present in x / out
   int cpl;                    // channels per lane
+  int sub;                    // warps that share one staged chunk side by side (chunk = 32 * cpl * sub channels)
+  int nroles;                 // forward kernel: warps per chunk column, specialised by output degree
+  int role_of_l3[kMaxFastL + 1];
   int chunks;                 // channel chunks per feature block
   int ch;                     // channels per block (uniform)
   int X, Y, O, W;
@@ -133,7 +136,8 @@ struct luna_uvu_plan {
 
   bool fast_ok = false;
   bool force_generic = false;
-  luna::FastMeta fast{};
+  luna::FastMeta fast{};   // per-warp stage layout (source-major kernel)
+  luna::FastMeta fastc{};  // per-CTA stage layout (destination-major kernel)
   std::vector<int> m_ptr, m_j;
   std::vector<double> m_c;
   std::vector<double> ell_c;

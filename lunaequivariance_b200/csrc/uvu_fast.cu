@@ -7,29 +7,36 @@
 namespace luna {
 namespace fastk {
 
-// Warps per CTA and stages per warp.  The kernels hide per-edge latency with resident warps, so the policy
-// maximises CTAs per SM first (up to 4 CTAs of 4 warps), then stages (3 preferred over 2); if one CTA of 4 warps
-// with two stages does not fit, the CTA shrinks.  Returns 0 if even one warp with two stages does not fit.
+// Warps per CTA (at most 8), CTAs per SM and stages per warp (2 or 3).  The kernels hide per-edge latency with
+// resident warps, so the policy maximises warps per SM (up to 16); ties go to more stages, then to fewer CTAs.
+// Returns 0 if even one warp with two stages does not fit.
 int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
                   size_t* block_bytes, int* warps) {
   int max_ctas = 4;
   if (const char* knob = std::getenv("LUNA_B200_MAX_CTAS")) max_ctas = std::max(1, std::atoi(knob));
-  for (int w = kWarps; w >= 1; --w) {
-    for (int ctas = max_ctas; ctas >= 1; --ctas) {
-      const size_t budget = static_cast<size_t>(max_smem_optin + 1024) / ctas - 1024;  // 1 KB reserved per CTA
-      for (int stages = 3; stages >= 2; --stages) {
+  int best_score = 0, best_stages = 0, best_warps = 0, best_ctas = 0;
+  size_t best_bytes = 0;
+  for (int ctas = 1; ctas <= max_ctas; ++ctas) {
+    const size_t budget = static_cast<size_t>(max_smem_optin + 1024) / ctas - 1024;  // 1 KB reserved per CTA
+    for (int w = 1; w <= kMaxWarps; ++w) {
+      for (int stages = 2; stages <= 3; ++stages) {
         const size_t bytes = shared_bytes + w * (stages * stage_bytes + fixed_bytes);
-        if (bytes <= budget) {
-          *block_bytes = bytes;
-          *warps = w;
-          return stages;
+        if (bytes > budget) continue;
+        const int score = std::min(16, w * ctas) * 4 + (stages - 2) * 2 + (ctas == 1 ? 1 : 0);
+        if (score > best_score) {
+          best_score = score;
+          best_stages = stages;
+          best_warps = w;
+          best_ctas = ctas;
+          best_bytes = bytes;
         }
       }
     }
   }
-  *block_bytes = 0;
-  *warps = 0;
-  return 0;
+  (void)best_ctas;
+  *block_bytes = best_bytes;
+  *warps = best_warps;
+  return best_stages;
 }
 
 // Explicit instantiations live in uvu_fast_fwd_*.cu so that they compile in parallel.
@@ -61,7 +68,11 @@ int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which) {
   const size_t elem = plan->dtype == LUNA_F64 ? 8 : 4;
   size_t fixed, stage;
   if (which == 0) {
-    fixed = static_cast<size_t>(f.m_total) * elem + 32 * elem + fastk::kMaxStages * sizeof(uint64_t);
+    if (plan->dtype == LUNA_F64)
+      fixed = f.cpl == 2 ? fastk::fwd_fixed_bytes<double, 2>(f) : fastk::fwd_fixed_bytes<double, 1>(f);
+    else
+      fixed = f.cpl == 4 ? fastk::fwd_fixed_bytes<float, 4>(f)
+                         : (f.cpl == 2 ? fastk::fwd_fixed_bytes<float, 2>(f) : fastk::fwd_fixed_bytes<float, 1>(f));
     stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * elem;
   } else {
     fixed = plan->dtype == LUNA_F64 ? fastk::bwd_fixed_bytes<double>(f) : fastk::bwd_fixed_bytes<float>(f);

@@ -23,9 +23,10 @@
 namespace luna {
 namespace fastk {
 
-constexpr int kWarps = 4;           // warps per CTA; each warp streams its own edge range
+constexpr int kWarps = 4;           // default warps per CTA; each warp streams its own edge range
+constexpr int kMaxWarps = 8;        // upper bound when shared memory allows only one CTA per SM
 constexpr int kMaxStages = 4;
-constexpr uint32_t kWaitLimit = 1u << 20;  // bounded mbarrier polling
+constexpr uint32_t kWaitLimit = 1u << 20;   // bounded mbarrier polling: tries per wait
 
 // ---- shared-memory barriers and bulk copies -------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -52,7 +53,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Polls with an iteration limit; returns false if the barrier never completed.
+// Polls with an iteration limit; returns false if the barrier never completed.  (A suspend-time hint on try_wait
+// was measured to delay the wake-up by the full hint, so none is given.)
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
   for (uint32_t spin = 0; spin < kWaitLimit; ++spin)
     if (mbar_try_wait(bar, parity)) return true;
@@ -196,6 +198,41 @@ __device__ __forceinline__ void compute_m(const T* ell_c, const unsigned char* e
     T a = ell_c[m] * ybuf[ell_j[m]];
     for (int t = 1; t < m_terms; ++t) a = fma(ell_c[t * m_total + m], ybuf[ell_j[t * m_total + m]], a);
     mbuf[m] = a;
+  }
+}
+
+// FP32 with an even number of channels per lane uses packed two-wide arithmetic; everything else the scalar path.
+template <typename T, int CPL>
+struct UsePairs {
+  static constexpr bool value = sizeof(T) == 4 && (CPL % 2 == 0);
+};
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+
+// One warp's share of the coupling-matrix computation when `parts` warps split the entries: warp `part` handles
+// entries (r * parts + part) * 32 + lane.  Two entries per trip with all loads issued before the arithmetic;
+// indices are clamped so the loads are unconditional and only the stores are predicated.  Requires exactly two
+// (zero-padded) terms per entry.  With DUP every entry is stored twice, (m, m), ready for packed arithmetic.
+template <typename T, bool DUP>
+__device__ __forceinline__ void compute_m_share(const T* ell_c, const unsigned char* ell_j, const T* ybuf, T* mbuf,
+                                                int m_total, int part, int parts, int lane) {
+  const int stride = 32 * parts;
+#pragma unroll 1
+  for (int m0 = part * 32 + lane; m0 < m_total; m0 += 2 * stride) {
+    const int m1 = m0 + stride;
+    const int i1 = m1 < m_total ? m1 : m0;
+    const unsigned ja0 = ell_j[m0], jb0 = ell_j[m_total + m0], ja1 = ell_j[i1], jb1 = ell_j[m_total + i1];
+    const T ca0 = ell_c[m0], cb0 = ell_c[m_total + m0], ca1 = ell_c[i1], cb1 = ell_c[m_total + i1];
+    const T r0 = fma(cb0, ybuf[jb0], ca0 * ybuf[ja0]);
+    const T r1 = fma(cb1, ybuf[jb1], ca1 * ybuf[ja1]);
+    if constexpr (DUP) {
+      Vec<T, 2> v0{{r0, r0}}, v1{{r1, r1}};
+      reinterpret_cast<Vec<T, 2>*>(mbuf)[m0] = v0;
+      if (m1 < m_total) reinterpret_cast<Vec<T, 2>*>(mbuf)[m1] = v1;
+    } else {
+      mbuf[m0] = r0;
+      if (m1 < m_total) mbuf[m1] = r1;
+    }
   }
 }
 

@@ -77,7 +77,7 @@ __device__ __forceinline__ void flush_tile(const T* red, T* gbuf, int count, int
 }
 
 template <typename T, int CPL, int LX, int LO>
-__global__ void __launch_bounds__(kWarps * 32, 1) fast_bwd_kernel(const __grid_constant__ BwdParams<T> P) {
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __grid_constant__ BwdParams<T> P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const FastMeta& F = P.meta;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

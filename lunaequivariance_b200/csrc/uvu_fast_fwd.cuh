@@ -2,12 +2,18 @@
 //
 // One warp owns a contiguous range of destination nodes (balanced by edge count) and therefore a contiguous range
 // of the destination-sorted edge list: a warp-segmented reduction with register accumulators and no atomics.  Per
-// edge, one elected lane issues 1-D bulk copies (cp.async.bulk, completion on an mbarrier) of the edge's weight
-// row and of the gathered x[src] row into the warp's ring of shared-memory stages; the warp then reads them with
-// 128-bit shared loads while later edges are in flight.  A lane owns CPL consecutive channels of every block.
+// edge, lanes issue 1-D bulk copies (cp.async.bulk, completion on an mbarrier) of the edge's weight row and of the
+// gathered x[src] row into the warp's ring of shared-memory stages; the warp then reads them with 128-bit shared
+// loads while later edges are in flight.  A lane owns CPL consecutive channels of every block.
+//
+// FP32 arithmetic runs on packed two-wide FMAs (fma.rn.f32x2): on B200 the scalar FFMA rate is about 0.7 of the
+// packed rate, and packing halves the instruction count of the loop, which is what limits this kernel (issue slots
+// and instruction-cache footprint), not bytes.  Two consecutive channels of a lane form a pair; the per-edge
+// coupling matrices are stored duplicated (m, m) in shared memory so that they arrive as ready-made pairs.
 #pragma once
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "uvu_fast.cuh"
 
@@ -31,15 +37,18 @@ struct FwdParams {
   int accumulate;
 };
 
-template <typename T>
-__host__ __device__ inline size_t fwd_warp_bytes(const FastMeta& f, int stages) {
-  const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
-  return stages * stage + static_cast<size_t>(f.m_total) * sizeof(T) + 32 * sizeof(T) + kMaxStages * sizeof(uint64_t);
+template <typename T, int CPL>
+__host__ __device__ inline size_t fwd_fixed_bytes(const FastMeta& f) {
+  // M buffer (duplicated entries on the packed path), y row, barriers
+  const size_t m_elems = static_cast<size_t>(f.m_total) * (UsePairs<T, CPL>::value ? 2 : 1);
+  return (m_elems + 32) * sizeof(T) + kMaxStages * sizeof(uint64_t);
 }
 
 template <typename T, int CPL, int LX, int LO>
-__global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_constant__ FwdParams<T> P) {
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_fwd_kernel(const __grid_constant__ FwdParams<T> P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr bool kPairs = UsePairs<T, CPL>::value;
+  constexpr int NP = CPL / 2;  // channel pairs per lane (packed path)
   const FastMeta& F = P.meta;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int stages = P.stages;
@@ -47,10 +56,11 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
   const T* ell_c;
   const unsigned char* ell_j;
   load_ell<T>(smem_raw, P.ell_c, P.ell_j, F.m_total, F.m_terms, &ell_c, &ell_j);
-  unsigned char* base = smem_raw + ell_bytes<T>(F.m_total, F.m_terms) + static_cast<size_t>(warp) * fwd_warp_bytes<T>(F, stages);
+  const size_t warp_bytes = static_cast<size_t>(stages) * stage_elems * sizeof(T) + fwd_fixed_bytes<T, CPL>(F);
+  unsigned char* base = smem_raw + ell_bytes<T>(F.m_total, F.m_terms) + static_cast<size_t>(warp) * warp_bytes;
   T* stage_mem = reinterpret_cast<T*>(base);
   T* mbuf = stage_mem + static_cast<size_t>(stages) * stage_elems;
-  T* ybuf = mbuf + F.m_total;
+  T* ybuf = mbuf + F.m_total * (kPairs ? 2 : 1);
   uint64_t* bars = reinterpret_cast<uint64_t*>(ybuf + 32);
 
   if (lane == 0) {
@@ -71,23 +81,26 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
   if (n_lo >= n_hi) return;
   const int64_t e_begin = P.dst_rowptr[n_lo], e_end = P.dst_rowptr[n_hi];
 
+  // Lane `pi` issues copy piece `pi` of every edge; its description stays in registers.
   const uint32_t stage_bytes = static_cast<uint32_t>(stage_elems * sizeof(T));
   const int n_pieces = F.n_w_pieces + F.n_x_pieces;
+  const bool piece_is_w = lane < F.n_w_pieces;
+  int64_t piece_goff = 0;
+  int piece_soff = 0;
+  uint32_t piece_bytes = 0;
+  if (lane < n_pieces) {
+    const CopyPiece pc = piece_is_w ? F.pieces_w[lane] : F.pieces_x[lane - F.n_w_pieces];
+    piece_goff = pc.g_off + static_cast<int64_t>(c0) * pc.comp;
+    piece_soff = pc.s_off + (piece_is_w ? 0 : F.w_stage_elems);
+    piece_bytes = static_cast<uint32_t>(pc.n * sizeof(T));
+  }
   auto issue = [&](int64_t e, int64_t s_node, int s) {
     uint64_t* bar = &bars[s];
     if (lane == 0) mbar_arrive_expect_tx(bar, stage_bytes);
     __syncwarp();
-    T* dst = stage_mem + static_cast<size_t>(s) * stage_elems;
-    for (int pi = lane; pi < n_pieces; pi += 32) {
-      if (pi < F.n_w_pieces) {
-        const CopyPiece pc = F.pieces_w[pi];
-        bulk_copy_g2s(dst + pc.s_off, P.w + e * F.W + pc.g_off + c0 * pc.comp,
-                      static_cast<uint32_t>(pc.n * sizeof(T)), bar);
-      } else {
-        const CopyPiece pc = F.pieces_x[pi - F.n_w_pieces];
-        bulk_copy_g2s(dst + F.w_stage_elems + pc.s_off, P.x + s_node * F.X + pc.g_off + c0 * pc.comp,
-                      static_cast<uint32_t>(pc.n * sizeof(T)), bar);
-      }
+    if (lane < n_pieces) {
+      const T* from = piece_is_w ? P.w + e * F.W + piece_goff : P.x + s_node * F.X + piece_goff;
+      bulk_copy_g2s(stage_mem + static_cast<size_t>(s) * stage_elems + piece_soff, from, piece_bytes, bar);
     }
   };
 
@@ -97,20 +110,19 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
   int src_ahead = e_begin + stages < e_end ? P.src[e_begin + stages] : 0;
 
   T y_next = (lane < F.Y && e_begin < e_end) ? P.y[e_begin * F.Y + lane] : T(0);
-  constexpr int XR = (LX + 1) * (LX + 1) * CPL;
   constexpr int AR = (LO + 1) * (LO + 1) * CPL;
-  T acc[AR];
+  T acc[AR];  // packed path: viewed as pairs, element (l3, k, pair) at l3*l3*CPL + (k*NP + pair)*2
   int64_t e = e_begin;
-  uint32_t it = 0;
+  int s = 0;
+  uint32_t parity = 0;
   bool alive = true;
 
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t ee = P.dst_rowptr[n + 1];
 #pragma unroll
     for (int a = 0; a < AR; ++a) acc[a] = T(0);
-    for (; e < ee; ++e, ++it) {
-      const int s = it % stages;
-      const uint32_t parity = (it / stages) & 1u;
+#pragma unroll 1
+    for (; e < ee; ++e) {
       if (!mbar_wait_bounded(&bars[s], parity)) {
         if (lane == 0) atomicExch(P.status, 1);
         alive = false;
@@ -121,38 +133,54 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
       // coupling matrices of this edge
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
-      compute_m<T>(ell_c, ell_j, F.m_terms, ybuf, mbuf, F.m_total, lane);
+      compute_m_share<T, kPairs>(ell_c, ell_j, ybuf, mbuf, F.m_total, 0, 1, lane);
       if (e + 1 < e_end && lane < F.Y) y_next = P.y[(e + 1) * F.Y + lane];
       __syncwarp();
-      // this lane's channels of the gathered x row
-      T xr[XR];
+
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         constexpr int d1 = 2 * l1 + 1;
-        if (F.x_off[l1] >= 0) load_vectors<T, CPL, d1>(xs + F.xs_off[l1] + lane * (CPL * d1), &xr[l1 * l1 * CPL]);
-      });
-      static_for<0, LX + 1>([&](auto l1c) {
-        constexpr int l1 = decltype(l1c)::value;
-        constexpr int d1 = 2 * l1 + 1;
+        if (F.x_off[l1] < 0) return;
+        T xl[CPL * d1];
+        load_vectors<T, CPL, d1>(xs + F.xs_off[l1] + lane * (CPL * d1), xl);
         static_for<0, LO + 1>([&](auto l3c) {
           constexpr int l3 = decltype(l3c)::value;
           constexpr int d3 = 2 * l3 + 1;
           const int q_end = F.pair_ptr[l3 * (kMaxFastL + 1) + l1 + 1];
+#pragma unroll 1
           for (int q = F.pair_ptr[l3 * (kMaxFastL + 1) + l1]; q < q_end; ++q) {
             T wv[CPL];
             load_vectors<T, CPL, 1>(ws + F.w_soff[q] + lane * CPL, wv);
-            T mr[d1 * d3];
-            load_matrix<T, d1 * d3>(mbuf + F.m_off[q], mr);
-            const T* xl = &xr[l1 * l1 * CPL];
             T* al = &acc[l3 * l3 * CPL];
+            if constexpr (kPairs) {
+              // matrix entries arrive duplicated: mr2[m] = (M[m], M[m])
+              float2 mr2[d1 * d3];
+              load_matrix<T, 2 * d1 * d3>(mbuf + 2 * F.m_off[q], reinterpret_cast<T*>(mr2));
 #pragma unroll
-            for (int c = 0; c < CPL; ++c) {
+              for (int p = 0; p < NP; ++p) {
+                const float2 w2 = make_float2(wv[2 * p], wv[2 * p + 1]);
 #pragma unroll
-              for (int k = 0; k < d3; ++k) {
-                T t = mr[k] * xl[c * d1];
+                for (int k = 0; k < d3; ++k) {
+                  float2 t = mul2(mr2[k], make_float2(xl[(2 * p) * d1], xl[(2 * p + 1) * d1]));
 #pragma unroll
-                for (int i = 1; i < d1; ++i) t = fma(mr[i * d3 + k], xl[c * d1 + i], t);
-                al[c * d3 + k] = fma(wv[c], t, al[c * d3 + k]);
+                  for (int i = 1; i < d1; ++i)
+                    t = fma2(mr2[i * d3 + k], make_float2(xl[(2 * p) * d1 + i], xl[(2 * p + 1) * d1 + i]), t);
+                  float2* a2 = reinterpret_cast<float2*>(al) + (k * NP + p);
+                  *a2 = fma2(w2, t, *a2);
+                }
+              }
+            } else {
+              T mr[d1 * d3];
+              load_matrix<T, d1 * d3>(mbuf + F.m_off[q], mr);
+#pragma unroll
+              for (int c = 0; c < CPL; ++c) {
+#pragma unroll
+                for (int k = 0; k < d3; ++k) {
+                  T t = mr[k] * xl[c * d1];
+#pragma unroll
+                  for (int i = 1; i < d1; ++i) t = fma(mr[i * d3 + k], xl[c * d1 + i], t);
+                  al[c * d3 + k] = fma(wv[c], t, al[c * d3 + k]);
+                }
               }
             }
           }
@@ -162,6 +190,10 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
       const int src_now = src_ahead;
       if (e + stages + 1 < e_end) src_ahead = P.src[e + stages + 1];
       if (e + stages < e_end) issue(e + stages, src_now, s);
+      if (++s == stages) {
+        s = 0;
+        parity ^= 1u;
+      }
     }
     if (!alive) break;
     // flush the node's accumulators
@@ -171,20 +203,38 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fast_fwd_kernel(const __grid_c
       if (F.o_off[l3] >= 0) {
         T* dst = P.out + n * F.O + F.o_off[l3] + c0 * d3 + lane * (CPL * d3);
         T* al = &acc[l3 * l3 * CPL];
+        T row[CPL * d3];  // memory order: channel-major, component-minor
+        if constexpr (kPairs) {
+#pragma unroll
+          for (int p = 0; p < NP; ++p)
+#pragma unroll
+            for (int k = 0; k < d3; ++k) {
+              row[(2 * p) * d3 + k] = al[(k * NP + p) * 2];
+              row[(2 * p + 1) * d3 + k] = al[(k * NP + p) * 2 + 1];
+            }
+        } else {
+#pragma unroll
+          for (int a = 0; a < CPL * d3; ++a) row[a] = al[a];
+        }
         if (P.accumulate) {
           T old[CPL * d3];
           load_vectors<T, CPL, d3>(dst, old);
 #pragma unroll
-          for (int a = 0; a < CPL * d3; ++a) al[a] += old[a];
+          for (int a = 0; a < CPL * d3; ++a) row[a] += old[a];
         }
-        store_vectors<T, CPL, d3>(dst, al);
+        store_vectors<T, CPL, d3>(dst, row);
       }
     });
   }
   if (!alive) {
     // let copies that are still in flight land before the CTA's shared memory is released
-    for (int d = 1; d < stages; ++d)
-      if (e + d < e_end) mbar_wait_bounded(&bars[(it + d) % stages], ((it + d) / stages) & 1u);
+    for (int d = 1; d < stages; ++d) {
+      if (++s == stages) {
+        s = 0;
+        parity ^= 1u;
+      }
+      if (e + d < e_end) mbar_wait_bounded(&bars[s], parity);
+    }
   }
 }
 
@@ -211,14 +261,14 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.num_edges = graph->num_edges;
   P.accumulate = accumulate ? 1 : 0;
   const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
-  const size_t fixed = static_cast<size_t>(f.m_total) * sizeof(T) + 32 * sizeof(T) + kMaxStages * sizeof(uint64_t);
   size_t block_bytes = 0;
   int nwarps = kWarps;
-  P.stages = choose_stages(stage, fixed, ell_bytes<T>(f.m_total, f.m_terms), dt.max_smem_optin, &block_bytes, &nwarps);
+  P.stages = choose_stages(stage, fwd_fixed_bytes<T, CPL>(f), ell_bytes<T>(f.m_total, f.m_terms), dt.max_smem_optin,
+                           &block_bytes, &nwarps);
   if (P.stages == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged forward needs more shared memory than the device has");
   auto kernel = fast_fwd_kernel<T, CPL, LX, LO>;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
-  // about 512 edges per warp, rounded to whole waves of two CTAs per SM
+  // about 512 edges per warp, rounded to whole waves of resident CTAs
   int64_t warps = std::max<int64_t>(1, ceil_div(graph->num_edges, 512));
   int64_t blocks = ceil_div(warps, nwarps);
   const int64_t wave = static_cast<int64_t>(dt.sm_count) * std::max<int64_t>(1, dt.max_smem_optin / std::max<size_t>(block_bytes, 1));
