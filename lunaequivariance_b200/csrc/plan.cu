@@ -45,14 +45,14 @@ void build_slots(const std::vector<PathRec>& paths, Key key, std::vector<SlotRec
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-// Fills the stage layout, path order and M program of `f` for `cpl` channels per lane and `sub` warps sharing one
-// staged chunk of 32 * cpl * sub channels.  Returns false if a limit of the staged kernels is exceeded.
-bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl, int sub, bool build_programs) {
+// Fills the stage layouts, path order and coupling-matrix program of `f` for `cpl` channels per lane.  Returns false
+// if a limit of the staged kernels is exceeded.
+bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl) {
   const auto& paths = plan->paths;
+  const int elem = plan->dtype == LUNA_F64 ? 8 : 4;
   const int ch = paths[0].ch;
   f.cpl = cpl;
-  f.sub = sub;
-  const int chw = 32 * cpl * sub;
+  const int chw = 32 * cpl;
   if (ch % chw != 0) return false;
   f.chunks = ch / chw;
   f.ch = ch;
@@ -62,7 +62,7 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl, int sub, bool build_
   f.W = plan->W;
   f.num_paths = static_cast<int>(paths.size());
 
-  // paths sorted by (l3, l1): all paths into one output degree are contiguous, also in the M buffer
+  // paths sorted by (l3, l1): all paths into one output degree are contiguous, also in the matrix buffer
   std::vector<int> order(paths.size());
   for (size_t i = 0; i < order.size(); ++i) order[i] = static_cast<int>(i);
   const int LO1 = kMaxFastL + 1;  // fixed stride so kernels compiled for larger degrees index the same table
@@ -73,7 +73,7 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl, int sub, bool build_
   for (int p : order) f.pair_ptr[pair_of(p) + 1]++;
   for (int i = 0; i < npairs; ++i) f.pair_ptr[i + 1] += f.pair_ptr[i];
 
-  // staged w layout follows the global weight order
+  // forward stage: w in global weight order
   std::vector<int> by_w(order.size());
   for (size_t q = 0; q < order.size(); ++q) by_w[q] = static_cast<int>(q);
   std::stable_sort(by_w.begin(), by_w.end(),
@@ -95,41 +95,60 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl, int sub, bool build_
     f.pieces_w[f.n_w_pieces++] = piece;
   }
   f.w_stage_elems = static_cast<int>(paths.size()) * chw;
-
-  auto layout_blocks = [&](const int* goff, int* soff, CopyPiece* pieces, int& npieces, int& total, int lmax) {
+  if (f.n_w_pieces + kMaxFastL + 1 > 32) return false;  // one lane issues one copy piece
+  {
     std::vector<int> ls;
-    for (int l = 0; l <= lmax; ++l)
-      if (goff[l] >= 0) ls.push_back(l);
-    std::sort(ls.begin(), ls.end(), [&](int a, int b) { return goff[a] < goff[b]; });
-    npieces = 0;
-    total = 0;
+    for (int l = 0; l <= f.LX; ++l)
+      if (f.x_off[l] >= 0) ls.push_back(l);
+    std::sort(ls.begin(), ls.end(), [&](int a, int b) { return f.x_off[a] < f.x_off[b]; });
+    f.n_x_pieces = 0;
+    f.x_stage_elems = 0;
     for (int l : ls) {
       const int d = 2 * l + 1;
-      soff[l] = total;
-      CopyPiece piece{goff[l], d, total, chw * d};
-      total += chw * d;
-      if (f.chunks == 1 && npieces > 0) {
-        CopyPiece& last = pieces[npieces - 1];
+      f.xs_off[l] = f.x_stage_elems;
+      CopyPiece piece{f.x_off[l], d, f.x_stage_elems, chw * d};
+      f.x_stage_elems += chw * d;
+      if (f.chunks == 1 && f.n_x_pieces > 0) {
+        CopyPiece& last = f.pieces_x[f.n_x_pieces - 1];
         if (last.g_off + last.n == piece.g_off && last.s_off + last.n == piece.s_off) {
           last.n += piece.n;
           continue;
         }
       }
-      pieces[npieces++] = piece;
+      f.pieces_x[f.n_x_pieces++] = piece;
     }
-  };
-  layout_blocks(f.x_off, f.xs_off, f.pieces_x, f.n_x_pieces, f.x_stage_elems, f.LX);
-  layout_blocks(f.o_off, f.gs_off, f.pieces_g, f.n_g_pieces, f.g_stage_elems, f.LO);
+  }
 
-  // per-edge M buffer (path matrices back to back, each padded to a multiple of 4 entries)
+  // backward units
+  f.nkinds = 0;
+  f.slot_elems = 0;
+  for (int l3 = 0; l3 <= kMaxFastL; ++l3) {
+    f.kind_of_l3[l3] = -1;
+    f.ug_soff[l3] = 0;
+    f.unit_elems[l3] = 0;
+    f.kind_l3[l3] = 0;
+  }
+  for (int l3 = 0; l3 <= f.LO; ++l3) {
+    if (f.o_off[l3] < 0) continue;
+    const int q0 = f.pair_ptr[l3 * LO1], q1 = f.pair_ptr[l3 * LO1 + LO1];
+    if (q1 - q0 + 1 > 32) return false;  // one lane issues one copy piece
+    for (int q = q0; q < q1; ++q) f.uw_soff[q] = (q - q0) * chw;
+    f.ug_soff[l3] = (q1 - q0) * chw;
+    const int kind = f.nkinds++;
+    f.kind_l3[kind] = l3;
+    f.kind_of_l3[l3] = kind;
+    f.unit_elems[kind] = (q1 - q0) * chw + chw * (2 * l3 + 1);
+    f.slot_elems = std::max(f.slot_elems, f.unit_elems[kind]);
+  }
+
+  // per-edge coupling matrices (path matrices back to back, rows padded to the even length d3 + 1, each matrix
+  // padded to a multiple of 4 entries)
   std::vector<int> m_ptr, m_j;
   std::vector<double> m_c;
   int total = 0;
-  std::vector<double> l3_cost(kMaxFastL + 1, 0.0);
   for (size_t q = 0; q < order.size(); ++q) {
     const PathRec& p = paths[order[q]];
     f.m_off[q] = total;
-    l3_cost[(p.d3 - 1) / 2] += p.d1 * p.d3 + p.d3 + 4;
     // terms sorted by k give (i, j) per k; rebuild a dense (i,k) -> list of (j, c)
     std::vector<std::vector<std::pair<int, double>>> cell(p.d1 * p.d3);
     for (int k = 0; k < p.d3; ++k)
@@ -137,43 +156,31 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl, int sub, bool build_
         const auto& term = plan->terms_k[t];
         cell[term.a * p.d3 + k].push_back({p.y_off + term.b, term.c});
       }
-    const int padded = round_up(p.d1 * p.d3, 4);
-    for (int m = 0; m < padded; ++m) {
+    const int d3p = p.d3 + 1;
+    for (int i = 0; i < p.d1; ++i)
+      for (int k = 0; k < d3p; ++k) {
+        m_ptr.push_back(static_cast<int>(m_j.size()));
+        if (k < p.d3)
+          for (auto [j, c] : cell[i * p.d3 + k]) {
+            m_j.push_back(j);
+            m_c.push_back(c);
+          }
+      }
+    total += p.d1 * d3p;
+    while (total % 4 != 0) {  // every matrix starts on a 16-byte boundary, also in FP32 without duplication
       m_ptr.push_back(static_cast<int>(m_j.size()));
-      if (m < p.d1 * p.d3)
-        for (auto [j, c] : cell[m]) {
-          m_j.push_back(j);
-          m_c.push_back(c);
-        }
+      ++total;
     }
-    total += padded;
   }
   m_ptr.push_back(static_cast<int>(m_j.size()));
   f.m_total = total;
   if (total > kMaxMEntries) return false;
 
-  // roles of the forward kernel: output degrees spread over at most three warps by cost, heaviest first
-  {
-    std::vector<int> present;
-    for (int l = 0; l <= kMaxFastL; ++l) {
-      f.role_of_l3[l] = 0;
-      if (f.o_off[l] >= 0) present.push_back(l);
-    }
-    std::sort(present.begin(), present.end(), [&](int a, int b) { return l3_cost[a] > l3_cost[b]; });
-    f.nroles = std::min<int>(3, static_cast<int>(present.size()));
-    std::vector<double> load(f.nroles, 0.0);
-    for (int l : present) {
-      const int r = static_cast<int>(std::min_element(load.begin(), load.end()) - load.begin());
-      f.role_of_l3[l] = r;
-      load[r] += l3_cost[l];
-    }
-  }
-  if (!build_programs) return true;
-
-  // the same program in padded (ELL) form for the kernels: term t of entry m at [t * m_total + m]
-  f.m_terms = 2;  // at least two (zero-padded) terms so that the kernels can read two unconditionally
-  for (int m = 0; m < total; ++m) f.m_terms = std::max(f.m_terms, m_ptr[m + 1] - m_ptr[m]);
-  if (f.m_terms > 2) return false;  // the staged kernels read exactly two terms per entry (enough for l <= 3)
+  // the program in padded (ELL) form for the kernels: term t of entry m at [t * m_total + m], exactly two
+  // (zero-padded) terms per entry, which is enough for l <= 3
+  f.m_terms = 2;
+  for (int m = 0; m < total; ++m)
+    if (m_ptr[m + 1] - m_ptr[m] > 2) return false;
   plan->ell_c.assign(static_cast<size_t>(f.m_terms) * total, 0.0);
   plan->ell_j.assign(static_cast<size_t>(f.m_terms) * total, 0);
   for (int m = 0; m < total; ++m)
@@ -197,11 +204,16 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl, int sub, bool build_
     }
   }
   plan->gy_ptr.push_back(static_cast<int>(plan->gy_m.size()));
+  f.gy_terms = static_cast<int>(plan->gy_m.size());
+  f.tb_gyc = 2 * total * elem;
+  f.tb_gyptr = f.tb_gyc + f.gy_terms * elem;
+  f.tb_gym = f.tb_gyptr + (plan->Y + 1) * 4;
+  f.tb_ellj = f.tb_gym + f.gy_terms * 2;
+  f.tb_bytes = round_up(f.tb_ellj + 2 * total, 16);
   return true;
 }
 
-// Decide whether the staged kernels apply and fill plan->fast (per-warp stages, used by the source-major kernel)
-// and plan->fastc (one stage ring per CTA shared by role warps, used by the destination-major kernel).
+// Decide whether the staged kernels apply and fill plan->fast.
 void analyse_fast(luna_uvu_plan* plan) {
   plan->fast_ok = false;
   const auto& paths = plan->paths;
@@ -213,7 +225,7 @@ void analyse_fast(luna_uvu_plan* plan) {
   if (plan->Y > 32) return;
   FastMeta f{};
   f.LX = f.LO = 0;
-  for (int l = 0; l <= kMaxFastL; ++l) f.x_off[l] = f.o_off[l] = f.xs_off[l] = f.gs_off[l] = -1;
+  for (int l = 0; l <= kMaxFastL; ++l) f.x_off[l] = f.o_off[l] = f.xs_off[l] = -1;
   for (const auto& p : paths) {
     if (p.ch != ch || p.w_stride != 1) return;
     const int l1 = (p.d1 - 1) / 2, l3 = (p.d3 - 1) / 2;
@@ -243,16 +255,8 @@ void analyse_fast(luna_uvu_plan* plan) {
     const int cap = std::atoi(knob);
     while (cap >= 1 && cpl > cap) cpl /= 2;
   }
-  FastMeta per_warp = f, per_cta = f;
-  if (!fill_layout(plan, per_warp, cpl, 1, true)) return;
-  // CTA layout: at most two channels per lane (small code), two warps side by side when the block is wide enough
-  const int cpl_c = std::min(cpl, 2);
-  int sub = ch % (32 * cpl_c * 2) == 0 ? 2 : 1;
-  if (const char* knob = std::getenv("LUNA_B200_SUB")) sub = std::max(1, std::atoi(knob));
-  if (!fill_layout(plan, per_cta, cpl_c, sub, false)) return;
-  per_cta.m_terms = per_warp.m_terms;
-  plan->fast = per_warp;
-  plan->fastc = per_cta;
+  if (!fill_layout(plan, f, cpl)) return;
+  plan->fast = f;
   plan->fast_ok = true;
 }
 
@@ -319,18 +323,26 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
     }
   }
   const size_t o_mc = append(mc.data(), mc.size());
-  const size_t o_gp = append(plan->gy_ptr.data(), plan->gy_ptr.size() * sizeof(int));
-  const size_t o_gm = append(plan->gy_m.data(), plan->gy_m.size() * sizeof(int));
-  std::vector<unsigned char> gc(plan->gy_c.size() * scalar);
-  for (size_t i = 0; i < plan->gy_c.size(); ++i) {
-    if (f64) {
-      std::memcpy(gc.data() + i * 8, &plan->gy_c[i], 8);
-    } else {
-      float v = static_cast<float>(plan->gy_c[i]);
-      std::memcpy(gc.data() + i * 4, &v, 4);
+  // backward kernel's blob
+  std::vector<unsigned char> blob;
+  if (plan->fast_ok) {
+    const FastMeta& f = plan->fast;
+    blob.assign(static_cast<size_t>(f.tb_bytes), 0);
+    std::memcpy(blob.data(), mc.data(), mc.size());
+    for (size_t i = 0; i < plan->gy_c.size(); ++i) {
+      if (f64) {
+        std::memcpy(blob.data() + f.tb_gyc + i * 8, &plan->gy_c[i], 8);
+      } else {
+        float v = static_cast<float>(plan->gy_c[i]);
+        std::memcpy(blob.data() + f.tb_gyc + i * 4, &v, 4);
+      }
+      const unsigned short m = static_cast<unsigned short>(plan->gy_m[i]);
+      std::memcpy(blob.data() + f.tb_gym + i * 2, &m, 2);
     }
+    std::memcpy(blob.data() + f.tb_gyptr, plan->gy_ptr.data(), plan->gy_ptr.size() * sizeof(int));
+    std::memcpy(blob.data() + f.tb_ellj, plan->ell_j.data(), plan->ell_j.size());
   }
-  const size_t o_gc = append(gc.data(), gc.size());
+  const size_t o_blob = append(blob.data(), blob.size());
 
   DeviceTables dt;
   dt.bytes = host.size();
@@ -358,9 +370,7 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   dt.terms_j = base + o_tj;
   dt.ell_j = base + o_mj;
   dt.ell_c = base + o_mc;
-  dt.gy_ptr = reinterpret_cast<const int*>(base + o_gp);
-  dt.gy_m = reinterpret_cast<const int*>(base + o_gm);
-  dt.gy_c = base + o_gc;
+  dt.bwd_tables = base + o_blob;
   LUNA_CUDA_CHECK(cudaDeviceGetAttribute(&dt.sm_count, cudaDevAttrMultiProcessorCount, device));
   LUNA_CUDA_CHECK(cudaDeviceGetAttribute(&dt.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   auto inserted = plan->device_tables.emplace(device, dt);

@@ -49,8 +49,7 @@ struct GenericTables {
 // ------------------------------------------------------------------------------------------------ staged ("fast") tables
 constexpr int kMaxFastPaths = 64;
 constexpr int kMaxFastL = 3;          // degrees 0..3 on x and out
-constexpr int kMaxPieces = 80;        // bulk-copy pieces per edge stage
-constexpr int kMaxMEntries = 512;     // per-edge M buffer entries (two warps x 8 entries per lane)
+constexpr int kMaxMEntries = 768;     // per-edge coupling-matrix entries (rows padded to an even length)
 
 struct CopyPiece {
   int g_off;   // element offset inside the global row for channel chunk 0
@@ -59,40 +58,43 @@ struct CopyPiece {
   int n;       // elements
 };
 
-// Everything the staged kernels need, small enough to travel as a kernel parameter.
+// Everything the staged kernels need, small enough to travel as a kernel parameter.  Paths are renumbered
+// q = 0.. in (l3, l1) order; the matrix of path q occupies entries m_off[q] + i * (d3 + 1) + k of the per-edge
+// coupling-matrix buffer (rows padded to the even length d3 + 1, matrices to a multiple of 4 entries; padding
+// entries are zero).
 struct FastMeta {
   int LX, LO;                 // highest degree present in x / out
   int cpl;                    // channels per lane
-  int sub;                    // warps that share one staged chunk side by side (chunk = 32 * cpl * sub channels)
-  int nroles;                 // forward kernel: warps per chunk column, specialised by output degree
-  int role_of_l3[kMaxFastL + 1];
-  int chunks;                 // channel chunks per feature block
+  int chunks;                 // channel chunks per feature block (a warp handles 32 * cpl channels)
   int ch;                     // channels per block (uniform)
   int X, Y, O, W;
   int num_paths;
   int x_off[kMaxFastL + 1];   // global offset of the degree-l block of x, -1 if absent
   int o_off[kMaxFastL + 1];
-  int xs_off[kMaxFastL + 1];  // offset of that block inside the staged x region (elements)
-  int gs_off[kMaxFastL + 1];  // offset inside the staged g region
-  int pair_ptr[(kMaxFastL + 1) * (kMaxFastL + 1) + 1];  // paths sorted by (l3, l1); index l3 * 4 + l1
-  int w_soff[kMaxFastPaths];  // offset of a path's channel chunk inside the staged w region
+  int pair_ptr[(kMaxFastL + 1) * (kMaxFastL + 1) + 1];  // first path of (l3, l1); index l3 * 4 + l1
   int w_goff[kMaxFastPaths];  // global weight offset of the path
-  int m_off[kMaxFastPaths];   // offset of the path's d1 x d3 matrix in the per-edge M buffer
-  int m_total;                // entries in the M buffer (padded)
-  int m_terms;                // terms per entry in the padded program (max over entries)
-  int w_stage_elems, x_stage_elems, g_stage_elems;
-  int n_w_pieces, n_x_pieces, n_g_pieces;
+  int m_off[kMaxFastPaths];
+  int m_total;                // entries in the coupling-matrix buffer (multiple of 4)
+  int m_terms;                // terms per entry in the padded program (always 2)
+  // forward kernel: one stage holds a whole edge, w in global order followed by the x blocks
+  int xs_off[kMaxFastL + 1];  // offset of the degree-l block inside the staged x region (elements)
+  int w_soff[kMaxFastPaths];  // offset of a path's channel chunk inside the staged w region
+  int w_stage_elems, x_stage_elems;
+  int n_w_pieces, n_x_pieces;
   CopyPiece pieces_w[kMaxFastPaths];
   CopyPiece pieces_x[kMaxFastL + 1];
-  CopyPiece pieces_g[kMaxFastL + 1];
-};
-
-// Device-resident program that turns one edge's y row into the M matrices: M[m] = sum_t c[t] * y[j[t]].
-template <typename T>
-struct MProgram {
-  const int* ptr;  // [m_total + 1]
-  const int* j;    // [terms]
-  const T* c;      // [terms]
+  // backward kernel: one ring slot holds one unit = (edge, output degree): the w chunks of the paths into that
+  // degree in q order, then the degree's block of the destination's g row
+  int nkinds;                       // output degrees present
+  int kind_l3[kMaxFastL + 1];       // degree of unit kind 0..nkinds-1 (ascending)
+  int kind_of_l3[kMaxFastL + 1];    // inverse, -1 if absent
+  int unit_elems[kMaxFastL + 1];    // elements of a unit of that kind
+  int slot_elems;                   // largest unit
+  int uw_soff[kMaxFastPaths];       // offset of a path's w chunk inside its unit
+  int ug_soff[kMaxFastL + 1];       // offset of the g block inside the unit of degree l3
+  // byte offsets inside the backward kernel's table blob (copied to shared memory by every CTA)
+  int tb_gyc, tb_gyptr, tb_gym, tb_ellj, tb_bytes;
+  int gy_terms;
 };
 
 // ------------------------------------------------------------------------------------------------ the plan
@@ -109,9 +111,10 @@ struct DeviceTables {
   const void *terms_k = nullptr, *terms_i = nullptr, *terms_j = nullptr;
   const unsigned char* ell_j = nullptr;  // [m_terms * m_total] y index of each term (padded form)
   const void* ell_c = nullptr;           // [m_terms * m_total] coefficient of each term, 0 for padding
-  const int* gy_ptr = nullptr;  // [Y + 1] program of the edge-attribute gradient
-  const int* gy_m = nullptr;
-  const void* gy_c = nullptr;
+  // backward kernel's tables in one blob: coefficients of the padded program, coefficients / row pointers /
+  // entry indices of the edge-attribute gradient's program (gy[j] = sum_t c[t] * G[m[t]]), y indices of the
+  // padded program; offsets in FastMeta::tb_*
+  const unsigned char* bwd_tables = nullptr;
   int sm_count = 0;
   int max_smem_optin = 0;
 };
@@ -136,10 +139,7 @@ struct luna_uvu_plan {
 
   bool fast_ok = false;
   bool force_generic = false;
-  luna::FastMeta fast{};   // per-warp stage layout (source-major kernel)
-  luna::FastMeta fastc{};  // per-CTA stage layout (destination-major kernel)
-  std::vector<int> m_ptr, m_j;
-  std::vector<double> m_c;
+  luna::FastMeta fast{};
   std::vector<double> ell_c;
   std::vector<unsigned char> ell_j;
   std::vector<int> gy_ptr, gy_m;

@@ -39,6 +39,37 @@ int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, i
   return best_stages;
 }
 
+int choose_slots(size_t slot_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin, int max_warps_by_regs,
+                 int nkinds, size_t* block_bytes, int* warps) {
+  int max_ctas = 4;
+  if (const char* knob = std::getenv("LUNA_B200_MAX_CTAS")) max_ctas = std::max(1, std::atoi(knob));
+  int slot_cap = std::min(kMaxSlots, 2 * nkinds);
+  if (const char* knob = std::getenv("LUNA_B200_SLOTS")) slot_cap = std::max(2, std::min(slot_cap, std::atoi(knob)));
+  const int slot_min = std::min(slot_cap, std::max(2, nkinds));
+  int best_score = 0, best_slots = 0, best_warps = 0;
+  size_t best_bytes = 0;
+  for (int ctas = 1; ctas <= max_ctas; ++ctas) {
+    const size_t budget = static_cast<size_t>(max_smem_optin + 1024) / ctas - 1024;  // 1 KB reserved per CTA
+    for (int w = 1; w <= kMaxWarps; ++w) {
+      if (w * ctas > std::max(1, max_warps_by_regs)) continue;
+      for (int slots = slot_min; slots <= slot_cap; ++slots) {
+        const size_t bytes = shared_bytes + w * (slots * slot_bytes + fixed_bytes);
+        if (bytes > budget) continue;
+        const int score = w * ctas * 64 + (slots - slot_min) * 4 + (max_ctas - ctas);
+        if (score > best_score) {
+          best_score = score;
+          best_slots = slots;
+          best_warps = w;
+          best_bytes = bytes;
+        }
+      }
+    }
+  }
+  *block_bytes = best_bytes;
+  *warps = best_warps;
+  return best_slots;
+}
+
 // Explicit instantiations live in uvu_fast_fwd_*.cu so that they compile in parallel.
 extern template int launch_fast_fwd<float, 1>(const luna_uvu_plan*, const DeviceTables&, const luna_graph*, const float*, const float*, const float*, float*, bool, cudaStream_t);
 extern template int launch_fast_fwd<float, 2>(const luna_uvu_plan*, const DeviceTables&, const luna_graph*, const float*, const float*, const float*, float*, bool, cudaStream_t);
@@ -75,8 +106,16 @@ int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which) {
                          : (f.cpl == 2 ? fastk::fwd_fixed_bytes<float, 2>(f) : fastk::fwd_fixed_bytes<float, 1>(f));
     stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * elem;
   } else {
-    fixed = plan->dtype == LUNA_F64 ? fastk::bwd_fixed_bytes<double>(f) : fastk::bwd_fixed_bytes<float>(f);
-    stage = static_cast<size_t>(f.w_stage_elems + f.g_stage_elems) * elem;
+    if (plan->dtype == LUNA_F64)
+      fixed = f.cpl == 2 ? fastk::bwd_fixed_bytes<double, 2>(f) : fastk::bwd_fixed_bytes<double, 1>(f);
+    else
+      fixed = f.cpl == 4 ? fastk::bwd_fixed_bytes<float, 4>(f)
+                         : (f.cpl == 2 ? fastk::bwd_fixed_bytes<float, 2>(f) : fastk::bwd_fixed_bytes<float, 1>(f));
+    size_t bytes = 0;
+    int warps = 0;
+    fastk::choose_slots(static_cast<size_t>(f.slot_elems) * elem, fixed, fastk::bwd_shared_bytes(f), kSmemLimit, 8,
+                        f.nkinds, &bytes, &warps);
+    return static_cast<int64_t>(bytes);
   }
   size_t bytes = 0;
   int warps = 0;

@@ -56,6 +56,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Polls with an iteration limit; returns false if the barrier never completed.  (A suspend-time hint on try_wait
 // was measured to delay the wake-up by the full hint, so none is given.)
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1
   for (uint32_t spin = 0; spin < kWaitLimit; ++spin)
     if (mbar_try_wait(bar, parity)) return true;
   return false;

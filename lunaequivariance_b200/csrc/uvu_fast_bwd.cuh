@@ -1,15 +1,20 @@
 // Staged source-major kernel: first derivatives gx, gy, gw in one pass over the weights.
 //
 // One warp owns a contiguous range of source nodes (balanced by out-edge count) and walks their out-edges through
-// the source CSR.  Per edge, bulk copies bring the weight row and the gathered g[dst] row into the warp's stage
-// ring.  With M^p = C^p . y[e] (see uvu_fast.cuh) each channel computes
+// the source CSR.  The stream is cut into units, one per (edge, output degree l3): the w chunks of the paths into
+// that degree plus the degree's block of the gathered g[dst] row.  Bulk copies bring units into the warp's ring of
+// shared-memory slots; a slot is refilled as soon as its unit is consumed, so the ring holds between one and two
+// edges and many warps fit on an SM.  With M^p = C^p . y[e] (see uvu_fast.cuh) each channel computes, one matrix
+// row i at a time,
 //     s_i   = sum_k M^p[i][k] g_k             (shared by the next two lines)
 //     gx_i += w_p * s_i                        (register accumulator of the source node, no atomics)
 //     gw_p  = sum_i x_i * s_i                  (streamed straight to global memory)
-//     G^p[i][k] += x_i * (w_p g_k)             (summed over the lane's channels, then over the warp)
-// The warp-wide sum of G runs through a padded shared-memory tile (write a column per lane, read a row per lane with
-// 128-bit loads, conflict-free), batched over the paths of one output degree.  Finally gy[e, j] = sum C^p_ijk G^p[i][k]
-// from a small per-j program.  Every output element is written by exactly one thread: deterministic.
+//     G^p[i][k] = sum over the lane's channels of x_i * (w_p g_k)
+// The warp-wide sum of G runs through a shared-memory tile of entry pairs: every lane writes its pair into the
+// pair's row (64/128-bit stores), one lane per row adds the 32 contributions (128-bit loads, rows padded against
+// bank conflicts), batched over up to 32 rows.  Finally gy[e, j] = sum C^p_ijk G^p[i][k] from a small per-j program
+// held in shared memory.  Every output element is written by exactly one thread in a fixed order: deterministic.
+// FP32 arithmetic with an even number of channels per lane uses packed two-wide FMAs over channel pairs.
 #pragma once
 
 #include <algorithm>
@@ -19,8 +24,15 @@
 namespace luna {
 namespace fastk {
 
-constexpr int kRedStride = 36;   // words per tile row: 32 lanes + 4 padding, keeps 128-bit row reads conflict-free
-constexpr int kRedEntries = 64;  // tile rows (entries of G summed per flush)
+constexpr int kMaxSlots = 8;    // ring slots per warp
+constexpr int kRedGroups = 32;  // rows of the reduction tile: one entry pair each, one row per lane at flush time
+
+// Elements per tile row: 32 lanes x 2 entries plus 16 bytes, so that lanes reading different rows with 128-bit loads
+// hit different banks.
+template <typename T>
+__host__ __device__ constexpr int red_stride() {
+  return 64 + 16 / static_cast<int>(sizeof(T));
+}
 
 template <typename T>
 struct BwdParams {
@@ -36,73 +48,178 @@ struct BwdParams {
   const int* dst;
   const int* src_rowptr;
   const int* edge_ids;
-  const unsigned char* ell_j;
-  const T* ell_c;
-  const int* gy_ptr;
-  const int* gy_m;
-  const T* gy_c;
+  const unsigned char* tables;  // blob described by FastMeta::tb_*
   int* status;
   int64_t num_src_nodes, num_edges;
-  int stages;
+  int slots;
   int acc_x, acc_y, acc_w;
 };
 
-template <typename T>
-__host__ __device__ inline size_t bwd_fixed_bytes(const FastMeta& f) {
-  // M buffer, G buffer, y row, reduction tile, barriers
-  return (2 * static_cast<size_t>(f.m_total) + 32 + static_cast<size_t>(kRedEntries) * kRedStride) * sizeof(T) +
-         kMaxStages * sizeof(uint64_t);
+// ---- arithmetic packets ---------------------------------------------------------------------------------------------
+// A lane's CPL channels are processed as NP packets of W channels: FP32 pairs (float2, packed FMAs) when CPL is even,
+// scalars otherwise.  Coupling-matrix entries are stored W times in shared memory so that one load fills a packet.
+template <typename T, int CPL>
+struct Pk {
+  using V = T;
+  static constexpr int W = 1, NP = CPL;
+};
+template <>
+struct Pk<float, 2> {
+  using V = float2;
+  static constexpr int W = 2, NP = 1;
+};
+template <>
+struct Pk<float, 4> {
+  using V = float2;
+  static constexpr int W = 2, NP = 2;
+};
+__device__ __forceinline__ float2 vfma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float vfma(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double vfma(double a, double b, double c) { return fma(a, b, c); }
+__device__ __forceinline__ float2 vmul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float vmul(float a, float b) { return a * b; }
+__device__ __forceinline__ double vmul(double a, double b) { return a * b; }
+__device__ __forceinline__ float hsum(float2 a) { return a.x + a.y; }
+__device__ __forceinline__ float hsum(float a) { return a; }
+__device__ __forceinline__ double hsum(double a) { return a; }
+__device__ __forceinline__ void put(float2& v, int c, float x) {
+  if (c == 0)
+    v.x = x;
+  else
+    v.y = x;
+}
+__device__ __forceinline__ void put(float& v, int, float x) { v = x; }
+__device__ __forceinline__ void put(double& v, int, double x) { v = x; }
+__device__ __forceinline__ float get(float2 v, int c) { return c == 0 ? v.x : v.y; }
+__device__ __forceinline__ float get(float v, int) { return v; }
+__device__ __forceinline__ double get(double v, int) { return v; }
+
+// Memory row [channel][component] (CPL x D, this lane's channels) -> packets [component][packet].
+template <typename T, int CPL, int D>
+__device__ __forceinline__ void load_packets(const T* p, typename Pk<T, CPL>::V* out) {
+  constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
+  T row[CPL * D];
+  load_vectors<T, CPL, D>(p, row);
+#pragma unroll
+  for (int c = 0; c < CPL; ++c)
+#pragma unroll
+    for (int i = 0; i < D; ++i) put(out[i * NP + c / W], c % W, row[c * D + i]);
+}
+template <typename T, int CPL, int D>
+__device__ __forceinline__ void unpack_packets(const typename Pk<T, CPL>::V* in, T* row) {
+  constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
+#pragma unroll
+  for (int c = 0; c < CPL; ++c)
+#pragma unroll
+    for (int i = 0; i < D; ++i) row[c * D + i] = get(in[i * NP + c / W], c % W);
 }
 
-// Sums tile rows [0, count) over the 32 lane columns and writes them to gbuf[0..count).
+// One row of a coupling matrix (D3P entries, each stored W times) from shared memory; every lane reads the same
+// address, so each load is one broadcast.  Rows start on 16-byte boundaries except in FP32 without duplication (8).
+template <typename T, int W, int D3P, typename V>
+__device__ __forceinline__ void load_matrix_row(const T* p, V* row) {
+  constexpr int N = W * D3P;
+  constexpr int per = (W * sizeof(T) == 4 ? 8 : 16) / sizeof(T);
+  static_assert(N % per == 0, "row length must be a whole number of vectors");
+  T flat[N];
+  const Vec<T, per>* v = reinterpret_cast<const Vec<T, per>*>(p);
+#pragma unroll
+  for (int n = 0; n < N / per; ++n) {
+    const Vec<T, per> t = v[n];
+#pragma unroll
+    for (int c = 0; c < per; ++c) flat[n * per + c] = t.a[c];
+  }
+#pragma unroll
+  for (int k = 0; k < D3P; ++k)
+#pragma unroll
+    for (int c = 0; c < W; ++c) put(row[k], c, flat[k * W + c]);
+}
+
+// Adds the 32 lane contributions of tile rows [0, groups) and writes the entry pairs to gbuf[0 .. 2 * groups).
+// Called from many places of the unrolled kernel, so it stays a real function: the hot loop has to fit the
+// instruction cache.
 template <typename T>
-__device__ __forceinline__ void flush_tile(const T* red, T* gbuf, int count, int lane) {
+__device__ __noinline__ void flush_tile(const T* red, T* gbuf, int groups, int lane) {
   __syncwarp();
-  for (int n = lane; n < count; n += 32) {
-    constexpr int per = 16 / sizeof(T);
-    const Vec<T, per>* row = reinterpret_cast<const Vec<T, per>*>(red + n * kRedStride);
-    T a0 = T(0), a1 = T(0);
+  if (lane < groups) {
+    const T* row = red + lane * red_stride<T>();
+    if constexpr (sizeof(T) == 4) {
+      float2 a0 = make_float2(0.f, 0.f), a1 = a0;
 #pragma unroll
-    for (int v = 0; v < 32 / per; v += 2) {
-      const Vec<T, per> p = row[v], q = row[v + 1];
-#pragma unroll
-      for (int c = 0; c < per; ++c) {
-        a0 += p.a[c];
-        a1 += q.a[c];
+      for (int v = 0; v < 16; ++v) {
+        const float4 q = reinterpret_cast<const float4*>(row)[v];
+        a0 = __fadd2_rn(a0, make_float2(q.x, q.y));
+        a1 = __fadd2_rn(a1, make_float2(q.z, q.w));
       }
+      reinterpret_cast<float2*>(gbuf)[lane] = __fadd2_rn(a0, a1);
+    } else {
+      double s0 = 0.0, s1 = 0.0, t0 = 0.0, t1 = 0.0;
+#pragma unroll
+      for (int v = 0; v < 32; v += 2) {
+        const double2 p = reinterpret_cast<const double2*>(row)[v], q = reinterpret_cast<const double2*>(row)[v + 1];
+        s0 += p.x;
+        s1 += p.y;
+        t0 += q.x;
+        t1 += q.y;
+      }
+      reinterpret_cast<double2*>(gbuf)[lane] = make_double2(s0 + t0, s1 + t1);
     }
-    gbuf[n] = a0 + a1;
   }
   __syncwarp();
 }
 
-template <typename T, int CPL, int LX, int LO>
+template <typename T, int CPL>
+__host__ __device__ inline size_t bwd_fixed_bytes(const FastMeta& f) {
+  // coupling matrices (W copies per entry), G buffer, reduction tile, y row, barriers
+  const size_t elems = static_cast<size_t>(f.m_total) * (Pk<T, CPL>::W + 1) +
+                       static_cast<size_t>(kRedGroups) * red_stride<T>() + 32;
+  return elems * sizeof(T) + kMaxSlots * sizeof(uint64_t);
+}
+// Per-CTA shared tables: the blob plus the w offsets of the paths.
+__host__ __device__ inline size_t bwd_shared_bytes(const FastMeta& f) {
+  return static_cast<size_t>(f.tb_bytes) + kMaxFastPaths * sizeof(int);
+}
+
+// WY: whether gy is produced (compiled in or out: the G work is half of the kernel).
+template <typename T, int CPL, int LX, int LO, bool WY>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __grid_constant__ BwdParams<T> P) {
+  using V = typename Pk<T, CPL>::V;
+  constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
+  constexpr int L1S = kMaxFastL + 1;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const FastMeta& F = P.meta;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int stages = P.stages;
-  const int stage_elems = F.w_stage_elems + F.g_stage_elems;
-  const size_t warp_bytes = static_cast<size_t>(stages) * stage_elems * sizeof(T) + bwd_fixed_bytes<T>(F);
-  const T* ell_c;
-  const unsigned char* ell_j;
-  load_ell<T>(smem_raw, P.ell_c, P.ell_j, F.m_total, F.m_terms, &ell_c, &ell_j);
-  unsigned char* base = smem_raw + ell_bytes<T>(F.m_total, F.m_terms) + static_cast<size_t>(warp) * warp_bytes;
-  T* stage_mem = reinterpret_cast<T*>(base);
-  T* mbuf = stage_mem + static_cast<size_t>(stages) * stage_elems;
-  T* gbuf = mbuf + F.m_total;
+  const int R = P.slots, nk = F.nkinds;
+  const int slot_elems = F.slot_elems;
+  constexpr int chw = 32 * CPL;
+  const int c0 = blockIdx.y * chw;
+
+  // CTA-wide tables
+  for (int i = threadIdx.x; i < F.tb_bytes / 16; i += blockDim.x)
+    reinterpret_cast<uint4*>(smem_raw)[i] = reinterpret_cast<const uint4*>(P.tables)[i];
+  int* wtab = reinterpret_cast<int*>(smem_raw + F.tb_bytes);  // global w offset of path q for this CTA's channels
+  for (int q = threadIdx.x; q < F.num_paths; q += blockDim.x) wtab[q] = F.w_goff[q] + c0;
+  __syncthreads();
+  const T* ell_c = reinterpret_cast<const T*>(smem_raw);
+  const T* gy_c = reinterpret_cast<const T*>(smem_raw + F.tb_gyc);
+  const int* gy_ptr = reinterpret_cast<const int*>(smem_raw + F.tb_gyptr);
+  const unsigned short* gy_m = reinterpret_cast<const unsigned short*>(smem_raw + F.tb_gym);
+  const unsigned char* ell_j = smem_raw + F.tb_ellj;
+
+  const size_t warp_bytes = static_cast<size_t>(R) * slot_elems * sizeof(T) + bwd_fixed_bytes<T, CPL>(F);
+  T* slots = reinterpret_cast<T*>(smem_raw + bwd_shared_bytes(F) + static_cast<size_t>(warp) * warp_bytes);
+  T* mbuf = slots + static_cast<size_t>(R) * slot_elems;
+  T* gbuf = mbuf + W * F.m_total;
   T* red = gbuf + F.m_total;
-  T* ybuf = red + kRedEntries * kRedStride;
+  T* ybuf = red + kRedGroups * red_stride<T>();
   uint64_t* bars = reinterpret_cast<uint64_t*>(ybuf + 32);
 
   if (lane == 0) {
-    for (int s = 0; s < stages; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < R; ++s) mbar_init(&bars[s], 1);
     fence_barrier_init();
   }
   __syncwarp();
 
-  const int chw = 32 * CPL;
-  const int c0 = blockIdx.y * chw;
   const int64_t E = P.num_edges, N = P.num_src_nodes;
   const int nwarps = blockDim.x >> 5;
   const int64_t total_warps = static_cast<int64_t>(gridDim.x) * nwarps;
@@ -112,136 +229,140 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
   const int64_t n_hi = gwarp == total_warps - 1 ? N : warp_lower_bound(P.src_rowptr, N, bound_hi, lane);
   if (n_lo >= n_hi) return;
   const int64_t p_begin = P.src_rowptr[n_lo], p_end = P.src_rowptr[n_hi];
-  const bool want_x = P.gx != nullptr, want_y = P.gy != nullptr, want_w = P.gw != nullptr;
+  const bool want_x = P.gx != nullptr, want_w = P.gw != nullptr;
+  constexpr bool want_y = WY;
+  const int64_t total_units = (p_end - p_begin) * nk;
 
-  const uint32_t stage_bytes = static_cast<uint32_t>(stage_elems * sizeof(T));
-  const int n_pieces = F.n_w_pieces + F.n_g_pieces;
-  auto issue = [&](int64_t e, int64_t d_node, int s) {
+  // Lane L copies the w chunk of the unit's L-th path; the lane after the last path copies the g block.
+  auto issue = [&](int kind, int64_t e, int64_t d_node, int s) {
     uint64_t* bar = &bars[s];
-    if (lane == 0) mbar_arrive_expect_tx(bar, stage_bytes);
+    const int l3 = F.kind_l3[kind];
+    const int q0 = F.pair_ptr[l3 * L1S], np = F.pair_ptr[l3 * L1S + L1S] - q0;
+    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(F.unit_elems[kind] * sizeof(T)));
     __syncwarp();
-    T* dstm = stage_mem + static_cast<size_t>(s) * stage_elems;
-    for (int pi = lane; pi < n_pieces; pi += 32) {
-      if (pi < F.n_w_pieces) {
-        const CopyPiece pc = F.pieces_w[pi];
-        bulk_copy_g2s(dstm + pc.s_off, P.w + e * F.W + pc.g_off + c0 * pc.comp,
-                      static_cast<uint32_t>(pc.n * sizeof(T)), bar);
-      } else {
-        const CopyPiece pc = F.pieces_g[pi - F.n_w_pieces];
-        bulk_copy_g2s(dstm + F.w_stage_elems + pc.s_off, P.g + d_node * F.O + pc.g_off + c0 * pc.comp,
-                      static_cast<uint32_t>(pc.n * sizeof(T)), bar);
-      }
+    T* to = slots + static_cast<size_t>(s) * slot_elems;
+    if (lane < np) {
+      bulk_copy_g2s(to + lane * chw, P.w + e * F.W + wtab[q0 + lane], static_cast<uint32_t>(chw * sizeof(T)), bar);
+    } else if (lane == np) {
+      const int d3 = 2 * l3 + 1;
+      bulk_copy_g2s(to + np * chw, P.g + d_node * F.O + F.o_off[l3] + c0 * d3,
+                    static_cast<uint32_t>(chw * d3 * sizeof(T)), bar);
     }
   };
-  for (int s = 0; s < stages; ++s)
-    if (p_begin + s < p_end) {
-      const int e0 = P.edge_ids[p_begin + s];
-      issue(e0, P.dst[e0], s);
-    }
-  // (edge id, destination) of the edges issued in the next two iterations, fetched early: the two loads depend on
-  // each other, so the id runs two iterations ahead and the destination one
-  int id_a1 = p_begin + stages < p_end ? P.edge_ids[p_begin + stages] : 0;
-  int dst_a1 = p_begin + stages < p_end ? P.dst[id_a1] : 0;
-  int id_a2 = p_begin + stages + 1 < p_end ? P.edge_ids[p_begin + stages + 1] : 0;
 
-  int64_t e_next = p_begin < p_end ? P.edge_ids[p_begin] : 0;
-  T y_next = (lane < F.Y && p_begin < p_end) ? P.y[e_next * F.Y + lane] : T(0);
-  constexpr int XR = (LX + 1) * (LX + 1) * CPL;
-  T xr[XR], gxr[XR];
+  // ids and destinations of the current and the next two edges; the id after those is fetched one step early
+  // because the destination load depends on it
+  auto id_at = [&](int64_t p) { return p < p_end ? P.edge_ids[p] : -1; };
+  auto dst_of = [&](int e) { return e >= 0 ? P.dst[e] : 0; };
+  int e0 = id_at(p_begin), e1 = id_at(p_begin + 1), e2 = id_at(p_begin + 2), e3 = id_at(p_begin + 3);
+  int d0 = dst_of(e0), d1n = dst_of(e1), d2n = dst_of(e2);
+  for (int v = 0; v < R && v < total_units; ++v) {
+    const int de = v / nk, kind = v - de * nk;  // R <= 2 * nk, so de is 0 or 1
+    issue(kind, de == 0 ? e0 : e1, de == 0 ? d0 : d1n, v);
+  }
+  T y_next = (lane < F.Y && e0 >= 0) ? P.y[static_cast<int64_t>(e0) * F.Y + lane] : T(0);
+
+  constexpr int XR = (LX + 1) * (LX + 1) * NP;
+  V xr[XR], gxr[XR];
   int64_t pos = p_begin;
-  uint32_t it = 0;
+  int64_t u = 0;  // unit being consumed
+  int s = 0;
+  uint32_t parity = 0;
   bool alive = true;
 
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t pe = P.src_rowptr[n + 1];
-    static_for<0, LX + 1>([&](auto l1c) {
-      constexpr int l1 = decltype(l1c)::value;
-      constexpr int d1 = 2 * l1 + 1;
-      if (F.x_off[l1] >= 0 && pos < pe)
-        load_vectors<T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1), &xr[l1 * l1 * CPL]);
-    });
+    if (pos < pe) {
+      static_for<0, LX + 1>([&](auto l1c) {
+        constexpr int l1 = decltype(l1c)::value;
+        constexpr int d1 = 2 * l1 + 1;
+        if (F.x_off[l1] >= 0)
+          load_packets<T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1), &xr[l1 * l1 * NP]);
+      });
+    }
 #pragma unroll
-    for (int a = 0; a < XR; ++a) gxr[a] = T(0);
+    for (int a = 0; a < XR; ++a) gxr[a] = V{};
 
-    for (; pos < pe; ++pos, ++it) {
-      const int s = it % stages;
-      if (!mbar_wait_bounded(&bars[s], (it / stages) & 1u)) {
-        if (lane == 0) atomicExch(P.status, 2);
-        alive = false;
-        break;
-      }
-      const int64_t e = e_next;
-      if (pos + 1 < p_end) e_next = P.edge_ids[pos + 1];
-      const T* ws = stage_mem + static_cast<size_t>(s) * stage_elems;
-      const T* gs = ws + F.w_stage_elems;
+#pragma unroll 1
+    for (; pos < pe && alive; ++pos) {
+      // coupling matrices of this edge, computed while its first unit may still be in flight
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
-      compute_m<T>(ell_c, ell_j, F.m_terms, ybuf, mbuf, F.m_total, lane);
-      if (pos + 1 < p_end && lane < F.Y) y_next = P.y[e_next * F.Y + lane];
+      compute_m_share<T, W == 2>(ell_c, ell_j, ybuf, mbuf, F.m_total, 0, 1, lane);
+      if (pos + 1 < p_end && lane < F.Y) y_next = P.y[static_cast<int64_t>(e1) * F.Y + lane];
       __syncwarp();
 
-      static_for<0, LO + 1>([&](auto l3c) {
+      // one unit per output degree present; the per-degree arithmetic is selected by a switch so that the wait and
+      // the refill exist once in the loop
+      auto unit_body = [&](auto l3c, const T* unit) {
         constexpr int l3 = decltype(l3c)::value;
         constexpr int d3 = 2 * l3 + 1;
-        const int q_first = F.pair_ptr[l3 * (kMaxFastL + 1)];
-        const int q_last = F.pair_ptr[l3 * (kMaxFastL + 1) + LX + 1];
-        if (q_first == q_last) return;
-        T gr[CPL * d3];
-        load_vectors<T, CPL, d3>(gs + F.gs_off[l3] + lane * (CPL * d3), gr);
-        int tile_base = F.m_off[q_first];  // first M/G index held in the reduction tile
-        int tile_end = tile_base;          // one past the last index written to the tile
+        constexpr int d3p = d3 + 1;
+        V g2[d3 * NP];
+        load_packets<T, CPL, d3>(unit + F.ug_soff[l3] + lane * (CPL * d3), g2);
+        const int q_first = F.pair_ptr[l3 * L1S];
+        int tile_base = F.m_off[q_first];  // first matrix entry held in the reduction tile
+        int tile_end = tile_base;          // one past the last entry written to the tile
         static_for<0, LX + 1>([&](auto l1c) {
           constexpr int l1 = decltype(l1c)::value;
           constexpr int d1 = 2 * l1 + 1;
-          constexpr int cnt = d1 * d3;
-          constexpr int cnt_pad = (cnt + 3) / 4 * 4;
-          const int q_end = F.pair_ptr[l3 * (kMaxFastL + 1) + l1 + 1];
-          for (int q = F.pair_ptr[l3 * (kMaxFastL + 1) + l1]; q < q_end; ++q) {
-            T wv[CPL];
-            load_vectors<T, CPL, 1>(ws + F.w_soff[q] + lane * CPL, wv);
-            T mr[cnt];
-            load_matrix<T, cnt>(mbuf + F.m_off[q], mr);
-            const T* xl = &xr[l1 * l1 * CPL];
-            T* gxl = &gxr[l1 * l1 * CPL];
-            T gwv[CPL];
-            {
-              // s_i = sum_k M[i][k] g_k for every channel first, so the matrix registers die early
-              T sv[CPL * d1];
-#pragma unroll
-              for (int c = 0; c < CPL; ++c) {
-#pragma unroll
-                for (int i = 0; i < d1; ++i) {
-                  T sacc = mr[i * d3] * gr[c * d3];
-#pragma unroll
-                  for (int k = 1; k < d3; ++k) sacc = fma(mr[i * d3 + k], gr[c * d3 + k], sacc);
-                  sv[c * d1 + i] = sacc;
-                }
-              }
-#pragma unroll
-              for (int c = 0; c < CPL; ++c) {
-#pragma unroll
-                for (int i = 0; i < d1; ++i) gxl[c * d1 + i] = fma(wv[c], sv[c * d1 + i], gxl[c * d1 + i]);
-                T dot = xl[c * d1] * sv[c * d1];
-#pragma unroll
-                for (int i = 1; i < d1; ++i) dot = fma(xl[c * d1 + i], sv[c * d1 + i], dot);
-                gwv[c] = dot;
-              }
-            }
-            T G[cnt];
+          constexpr int span = (d1 * d3p + 3) / 4 * 4;  // entries the matrix occupies
+          const int q_end = F.pair_ptr[l3 * L1S + l1 + 1];
+#pragma unroll 1
+          for (int q = F.pair_ptr[l3 * L1S + l1]; q < q_end; ++q) {
+            const int m_off = F.m_off[q];
+            V w2[NP];
+            load_packets<T, CPL, 1>(unit + F.uw_soff[q] + lane * CPL, w2);
+            const V* xl = &xr[l1 * l1 * NP];
+            V* gxl = &gxr[l1 * l1 * NP];
+            V wg[d3 * NP];
             if (want_y) {
 #pragma unroll
-              for (int c = 0; c < CPL; ++c) {
+              for (int a = 0; a < d3 * NP; ++a) wg[a] = vmul(w2[a % NP], g2[a]);
+              if (m_off + span - tile_base > 2 * kRedGroups) {  // tile full: reduce what it holds
+                flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
+                tile_base = m_off;
+              }
+            }
+            T* tile = red + ((m_off - tile_base) / 2) * red_stride<T>() + lane * 2;
+            V dot[NP];
+#pragma unroll
+            for (int p = 0; p < NP; ++p) dot[p] = V{};
+            const T* mrows = mbuf + W * m_off;
+#pragma unroll
+            for (int i = 0; i < d1; ++i) {
+              V mrow[d3p];
+              load_matrix_row<T, W, d3p, V>(mrows + i * (W * d3p), mrow);
+#pragma unroll
+              for (int p = 0; p < NP; ++p) {
+                V sv = vmul(mrow[0], g2[p]);
+#pragma unroll
+                for (int k = 1; k < d3; ++k) sv = vfma(mrow[k], g2[k * NP + p], sv);
+                gxl[i * NP + p] = vfma(w2[p], sv, gxl[i * NP + p]);
+                dot[p] = vfma(xl[i * NP + p], sv, dot[p]);
+              }
+              if (want_y) {
+                T grow[d3p];
 #pragma unroll
                 for (int k = 0; k < d3; ++k) {
-                  const T wg = wv[c] * gr[c * d3 + k];
+                  V acc = vmul(xl[i * NP], wg[k * NP]);
 #pragma unroll
-                  for (int i = 0; i < d1; ++i)
-                    G[i * d3 + k] = c == 0 ? xl[i] * wg : fma(xl[c * d1 + i], wg, G[i * d3 + k]);
+                  for (int p = 1; p < NP; ++p) acc = vfma(xl[i * NP + p], wg[k * NP + p], acc);
+                  grow[k] = hsum(acc);
+                }
+                grow[d3] = T(0);
+#pragma unroll
+                for (int kk = 0; kk < d3p / 2; ++kk) {
+                  Vec<T, 2> pr{{grow[2 * kk], grow[2 * kk + 1]}};
+                  *reinterpret_cast<Vec<T, 2>*>(tile + (i * (d3p / 2) + kk) * red_stride<T>()) = pr;
                 }
               }
             }
+            if (want_y) tile_end = m_off + d1 * d3p;
             if (want_w) {
-              T* dstw = P.gw + e * F.W + F.w_goff[q] + c0 + lane * CPL;
+              T gwv[CPL];
+              unpack_packets<T, CPL, 1>(dot, gwv);
+              T* dstw = P.gw + static_cast<int64_t>(e0) * F.W + F.w_goff[q] + c0 + lane * CPL;
               if (P.acc_w) {
                 T old[CPL];
                 load_vectors<T, CPL, 1>(dstw, old);
@@ -250,41 +371,80 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
               }
               store_vectors_streaming<T, CPL, 1>(dstw, gwv);
             }
-            if (want_y) {
-              if (F.m_off[q] + cnt_pad - tile_base > kRedEntries) {  // tile full: reduce what it holds
-                flush_tile<T>(red, gbuf + tile_base, tile_end - tile_base, lane);
-                tile_base = F.m_off[q];
-              }
-              T* col = red + (F.m_off[q] - tile_base) * kRedStride + lane;
-#pragma unroll
-              for (int m = 0; m < cnt; ++m) col[m * kRedStride] = G[m];
-              tile_end = F.m_off[q] + cnt;
-            }
           }
         });
-        if (want_y && tile_end > tile_base) flush_tile<T>(red, gbuf + tile_base, tile_end - tile_base, lane);
-      });
+        if (want_y && tile_end > tile_base) flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
+      };
+#pragma unroll 1
+      for (int kind = 0; kind < nk; ++kind) {
+        if (!mbar_wait_bounded(&bars[s], parity)) {
+          if (lane == 0) atomicExch(P.status, 2);
+          alive = false;
+          break;
+        }
+        const T* unit = slots + static_cast<size_t>(s) * slot_elems;
+        switch (F.kind_l3[kind]) {
+          case 0:
+            unit_body(std::integral_constant<int, 0>{}, unit);
+            break;
+          case 1:
+            if constexpr (LO >= 1) unit_body(std::integral_constant<int, 1>{}, unit);
+            break;
+          case 2:
+            if constexpr (LO >= 2) unit_body(std::integral_constant<int, 2>{}, unit);
+            break;
+          default:
+            if constexpr (LO >= 3) unit_body(std::integral_constant<int, 3>{}, unit);
+            break;
+        }
+        __syncwarp();  // every lane is done with this slot
+        if (u + R < total_units) {
+          int next = kind + R, de = 0;
+          if (next >= nk) {
+            next -= nk;
+            de = 1;
+          }
+          if (next >= nk) {
+            next -= nk;
+            de = 2;
+          }
+          issue(next, de == 0 ? e0 : (de == 1 ? e1 : e2), de == 0 ? d0 : (de == 1 ? d1n : d2n), s);
+        }
+        ++u;
+        if (++s == R) {
+          s = 0;
+          parity ^= 1u;
+        }
+      }
+      if (!alive) break;
 
       if (want_y) {
-        __syncwarp();
-        if (lane < F.Y) {
-          T acc = T(0);
-          const int t1 = __ldg(P.gy_ptr + lane + 1);
-          for (int t = __ldg(P.gy_ptr + lane); t < t1; ++t) acc = fma(__ldg(P.gy_c + t), gbuf[__ldg(P.gy_m + t)], acc);
+        // gy[e, j] = sum_t c[t] * G[m[t]]; two lanes share a j when the row is short enough
+        const int lpj = F.Y <= 16 ? 2 : 1;
+        const int j = lpj == 2 ? lane >> 1 : lane, h = lpj == 2 ? lane & 1 : 0;
+        T acc = T(0);
+        if (j < F.Y) {
+          const int t1 = gy_ptr[j + 1];
+          for (int t = gy_ptr[j] + h; t < t1; t += lpj) acc = fma(gy_c[t], gbuf[gy_m[t]], acc);
+        }
+        if (lpj == 2) acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        if (j < F.Y && h == 0) {
           if (P.gy_partial != nullptr) {
-            P.gy_partial[(static_cast<int64_t>(blockIdx.y) * E + e) * F.Y + lane] = acc;
+            P.gy_partial[(static_cast<int64_t>(blockIdx.y) * E + e0) * F.Y + j] = acc;
           } else {
-            T* dsty = P.gy + e * F.Y + lane;
+            T* dsty = P.gy + static_cast<int64_t>(e0) * F.Y + j;
             *dsty = P.acc_y ? *dsty + acc : acc;
           }
         }
+        __syncwarp();
       }
-      __syncwarp();
-      const int id_now = id_a1, dst_now = dst_a1;
-      id_a1 = id_a2;
-      if (pos + stages + 1 < p_end) dst_a1 = P.dst[id_a1];
-      if (pos + stages + 2 < p_end) id_a2 = P.edge_ids[pos + stages + 2];
-      if (pos + stages < p_end) issue(id_now, dst_now, s);
+      e0 = e1;
+      d0 = d1n;
+      e1 = e2;
+      d1n = d2n;
+      e2 = e3;
+      if (pos + 3 < p_end) d2n = P.dst[e2];
+      if (pos + 4 < p_end) e3 = P.edge_ids[pos + 4];
     }
     if (!alive) break;
     if (want_x) {
@@ -293,21 +453,28 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
         constexpr int d1 = 2 * l1 + 1;
         if (F.x_off[l1] >= 0) {
           T* dstx = P.gx + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1);
-          T* gxl = &gxr[l1 * l1 * CPL];
+          T row[CPL * d1];  // memory order: channel-major, component-minor
+          unpack_packets<T, CPL, d1>(&gxr[l1 * l1 * NP], row);
           if (P.acc_x) {
             T old[CPL * d1];
             load_vectors<T, CPL, d1>(dstx, old);
 #pragma unroll
-            for (int a = 0; a < CPL * d1; ++a) gxl[a] += old[a];
+            for (int a = 0; a < CPL * d1; ++a) row[a] += old[a];
           }
-          store_vectors<T, CPL, d1>(dstx, gxl);
+          store_vectors<T, CPL, d1>(dstx, row);
         }
       });
     }
   }
-  if (!alive) {
-    for (int d = 1; d < stages; ++d)
-      if (pos + d < p_end) mbar_wait_bounded(&bars[(it + d) % stages], ((it + d) / stages) & 1u);
+  if (!alive) {  // let copies that are still in flight land before the CTA's shared memory is released
+    const int64_t last = u + R < total_units ? u + R : total_units;
+    for (int64_t v = u + 1; v < last; ++v) {
+      if (++s == R) {
+        s = 0;
+        parity ^= 1u;
+      }
+      mbar_wait_bounded(&bars[s], parity);
+    }
   }
 }
 
@@ -322,8 +489,10 @@ __global__ void reduce_gy_partial(const T* __restrict__ partial, T* __restrict__
   gy[idx] = acc;
 }
 
-int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
-                  size_t* block_bytes, int* warps);
+// Picks ring slots per warp and warps per CTA: as many resident warps as registers and shared memory allow, each
+// with at least one whole edge (nkinds units) and at most two in its ring.  Returns the slot count, 0 if nothing fits.
+int choose_slots(size_t slot_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin, int max_warps_by_regs,
+                 int nkinds, size_t* block_bytes, int* warps);
 
 template <typename T, int CPL, int LX, int LO>
 int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
@@ -343,11 +512,7 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.dst = graph->dst;
   P.src_rowptr = graph->src_rowptr;
   P.edge_ids = graph->edge_ids_by_src;
-  P.ell_j = dt.ell_j;
-  P.ell_c = static_cast<const T*>(dt.ell_c);
-  P.gy_ptr = dt.gy_ptr;
-  P.gy_m = dt.gy_m;
-  P.gy_c = static_cast<const T*>(dt.gy_c);
+  P.tables = dt.bwd_tables;
   P.status = dt.status;
   P.num_src_nodes = graph->num_src_nodes > 0 ? graph->num_src_nodes : graph->num_nodes;
   P.num_edges = graph->num_edges;
@@ -363,12 +528,15 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     if (!aligned_to(scratch, 16)) return fail(LUNA_ERR_MISALIGNED, "scratch must be 16-byte aligned");
     P.gy_partial = static_cast<T*>(scratch);
   }
-  const size_t stage = static_cast<size_t>(f.w_stage_elems + f.g_stage_elems) * sizeof(T);
+  auto kernel = gy != nullptr ? fast_bwd_kernel<T, CPL, LX, LO, true> : fast_bwd_kernel<T, CPL, LX, LO, false>;
+  cudaFuncAttributes attr;
+  LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
+  const int regs_per_warp = (std::max(attr.numRegs, 1) * 32 + 511) / 512 * 512;
   size_t block_bytes = 0;
   int nwarps = kWarps;
-  P.stages = choose_stages(stage, bwd_fixed_bytes<T>(f), ell_bytes<T>(f.m_total, f.m_terms), dt.max_smem_optin, &block_bytes, &nwarps);
-  if (P.stages == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
-  auto kernel = fast_bwd_kernel<T, CPL, LX, LO>;
+  P.slots = choose_slots(static_cast<size_t>(f.slot_elems) * sizeof(T), bwd_fixed_bytes<T, CPL>(f), bwd_shared_bytes(f),
+                         dt.max_smem_optin, 65536 / regs_per_warp, f.nkinds, &block_bytes, &nwarps);
+  if (P.slots == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
   int64_t warps = std::max<int64_t>(1, ceil_div(graph->num_edges, 256));
   int64_t blocks = ceil_div(warps, nwarps);

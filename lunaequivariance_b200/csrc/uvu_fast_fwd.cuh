@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_fwd_kernel(const __gri
         static_for<0, LO + 1>([&](auto l3c) {
           constexpr int l3 = decltype(l3c)::value;
           constexpr int d3 = 2 * l3 + 1;
+          constexpr int d3p = d3 + 1;  // row stride of the coupling matrices
           const int q_end = F.pair_ptr[l3 * (kMaxFastL + 1) + l1 + 1];
 #pragma unroll 1
           for (int q = F.pair_ptr[l3 * (kMaxFastL + 1) + l1]; q < q_end; ++q) {
@@ -154,8 +155,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_fwd_kernel(const __gri
             T* al = &acc[l3 * l3 * CPL];
             if constexpr (kPairs) {
               // matrix entries arrive duplicated: mr2[m] = (M[m], M[m])
-              float2 mr2[d1 * d3];
-              load_matrix<T, 2 * d1 * d3>(mbuf + 2 * F.m_off[q], reinterpret_cast<T*>(mr2));
+              float2 mr2[d1 * d3p];
+              load_matrix<T, 2 * d1 * d3p>(mbuf + 2 * F.m_off[q], reinterpret_cast<T*>(mr2));
 #pragma unroll
               for (int p = 0; p < NP; ++p) {
                 const float2 w2 = make_float2(wv[2 * p], wv[2 * p + 1]);
@@ -164,21 +165,21 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_fwd_kernel(const __gri
                   float2 t = mul2(mr2[k], make_float2(xl[(2 * p) * d1], xl[(2 * p + 1) * d1]));
 #pragma unroll
                   for (int i = 1; i < d1; ++i)
-                    t = fma2(mr2[i * d3 + k], make_float2(xl[(2 * p) * d1 + i], xl[(2 * p + 1) * d1 + i]), t);
+                    t = fma2(mr2[i * d3p + k], make_float2(xl[(2 * p) * d1 + i], xl[(2 * p + 1) * d1 + i]), t);
                   float2* a2 = reinterpret_cast<float2*>(al) + (k * NP + p);
                   *a2 = fma2(w2, t, *a2);
                 }
               }
             } else {
-              T mr[d1 * d3];
-              load_matrix<T, d1 * d3>(mbuf + F.m_off[q], mr);
+              T mr[d1 * d3p];
+              load_matrix<T, d1 * d3p>(mbuf + F.m_off[q], mr);
 #pragma unroll
               for (int c = 0; c < CPL; ++c) {
 #pragma unroll
                 for (int k = 0; k < d3; ++k) {
                   T t = mr[k] * xl[c * d1];
 #pragma unroll
-                  for (int i = 1; i < d1; ++i) t = fma(mr[i * d3 + k], xl[c * d1 + i], t);
+                  for (int i = 1; i < d1; ++i) t = fma(mr[i * d3p + k], xl[c * d1 + i], t);
                   al[c * d3 + k] = fma(wv[c], t, al[c * d3 + k]);
                 }
               }
