@@ -7,67 +7,42 @@
 namespace luna {
 namespace fastk {
 
-// Warps per CTA (at most 8), CTAs per SM and stages per warp (2 or 3).  The kernels hide per-edge latency with
-// resident warps, so the policy maximises warps per SM (up to 16); ties go to more stages, then to fewer CTAs.
-// Returns 0 if even one warp with two stages does not fit.
-int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
-                  size_t* block_bytes, int* warps) {
+Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
+                           int regs_per_thread, int min_depth, int max_depth) {
   int max_ctas = 4;
   if (const char* knob = std::getenv("LUNA_B200_MAX_CTAS")) max_ctas = std::max(1, std::atoi(knob));
-  int best_score = 0, best_stages = 0, best_warps = 0, best_ctas = 0;
-  size_t best_bytes = 0;
+  if (const char* knob = std::getenv("LUNA_B200_DEPTH")) max_depth = std::max(min_depth, std::min(max_depth, std::atoi(knob)));
+  const int regs_per_warp = (std::max(regs_per_thread, 1) + 7) / 8 * 8 * 32;
+  const int warp_slots = std::max(1, 16384 / regs_per_warp);  // per sub-partition
+  Residency best;
+  int best_score = 0;
   for (int ctas = 1; ctas <= max_ctas; ++ctas) {
     const size_t budget = static_cast<size_t>(max_smem_optin + 1024) / ctas - 1024;  // 1 KB reserved per CTA
     for (int w = 1; w <= kMaxWarps; ++w) {
-      for (int stages = 2; stages <= 3; ++stages) {
-        const size_t bytes = shared_bytes + w * (stages * stage_bytes + fixed_bytes);
+      if (ctas * ((w + 3) / 4) > warp_slots) continue;
+      for (int depth = min_depth; depth <= max_depth; ++depth) {
+        const size_t bytes = shared_bytes + w * (depth * ring_bytes + fixed_bytes);
         if (bytes > budget) continue;
-        const int score = std::min(16, w * ctas) * 4 + (stages - 2) * 2 + (ctas == 1 ? 1 : 0);
+        const int score = w * ctas * 64 + (depth - min_depth) * 4 + (max_ctas - ctas);
         if (score > best_score) {
           best_score = score;
-          best_stages = stages;
-          best_warps = w;
-          best_ctas = ctas;
-          best_bytes = bytes;
+          best.depth = depth;
+          best.warps = w;
+          best.ctas = ctas;
+          best.block_bytes = bytes;
         }
       }
     }
   }
-  (void)best_ctas;
-  *block_bytes = best_bytes;
-  *warps = best_warps;
-  return best_stages;
+  return best;
 }
 
-int choose_slots(size_t slot_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin, int max_warps_by_regs,
-                 int nkinds, size_t* block_bytes, int* warps) {
-  int max_ctas = 4;
-  if (const char* knob = std::getenv("LUNA_B200_MAX_CTAS")) max_ctas = std::max(1, std::atoi(knob));
-  int slot_cap = std::min(kMaxSlots, 2 * nkinds);
-  if (const char* knob = std::getenv("LUNA_B200_SLOTS")) slot_cap = std::max(2, std::min(slot_cap, std::atoi(knob)));
-  const int slot_min = std::min(slot_cap, std::max(2, nkinds));
-  int best_score = 0, best_slots = 0, best_warps = 0;
-  size_t best_bytes = 0;
-  for (int ctas = 1; ctas <= max_ctas; ++ctas) {
-    const size_t budget = static_cast<size_t>(max_smem_optin + 1024) / ctas - 1024;  // 1 KB reserved per CTA
-    for (int w = 1; w <= kMaxWarps; ++w) {
-      if (w * ctas > std::max(1, max_warps_by_regs)) continue;
-      for (int slots = slot_min; slots <= slot_cap; ++slots) {
-        const size_t bytes = shared_bytes + w * (slots * slot_bytes + fixed_bytes);
-        if (bytes > budget) continue;
-        const int score = w * ctas * 64 + (slots - slot_min) * 4 + (max_ctas - ctas);
-        if (score > best_score) {
-          best_score = score;
-          best_slots = slots;
-          best_warps = w;
-          best_bytes = bytes;
-        }
-      }
-    }
-  }
-  *block_bytes = best_bytes;
-  *warps = best_warps;
-  return best_slots;
+int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count) {
+  const int64_t warps = std::max<int64_t>(1, ceil_div(num_edges, edges_per_warp(target)));
+  int64_t blocks = ceil_div(warps, r.warps);
+  const int64_t wave = static_cast<int64_t>(sm_count) * r.ctas;
+  if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
+  return blocks;
 }
 
 // Explicit instantiations live in uvu_fast_fwd_*.cu so that they compile in parallel.
@@ -97,32 +72,29 @@ int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which) {
   if (!plan->fast_ok) return 0;
   const FastMeta& f = plan->fast;
   const size_t elem = plan->dtype == LUNA_F64 ? 8 : 4;
-  size_t fixed, stage;
+  // an upper bound for callers that size things before a launch: the launch itself knows the register count
+  size_t fixed;
+  fastk::Residency r;
   if (which == 0) {
     if (plan->dtype == LUNA_F64)
       fixed = f.cpl == 2 ? fastk::fwd_fixed_bytes<double, 2>(f) : fastk::fwd_fixed_bytes<double, 1>(f);
     else
       fixed = f.cpl == 4 ? fastk::fwd_fixed_bytes<float, 4>(f)
                          : (f.cpl == 2 ? fastk::fwd_fixed_bytes<float, 2>(f) : fastk::fwd_fixed_bytes<float, 1>(f));
-    stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * elem;
+    const size_t shared = plan->dtype == LUNA_F64 ? fastk::ell_bytes<double>(f.m_total, f.m_terms)
+                                                  : fastk::ell_bytes<float>(f.m_total, f.m_terms);
+    r = fastk::choose_residency(static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * elem, fixed, shared, kSmemLimit,
+                                255, 2, 3);
   } else {
     if (plan->dtype == LUNA_F64)
       fixed = f.cpl == 2 ? fastk::bwd_fixed_bytes<double, 2>(f) : fastk::bwd_fixed_bytes<double, 1>(f);
     else
       fixed = f.cpl == 4 ? fastk::bwd_fixed_bytes<float, 4>(f)
                          : (f.cpl == 2 ? fastk::bwd_fixed_bytes<float, 2>(f) : fastk::bwd_fixed_bytes<float, 1>(f));
-    size_t bytes = 0;
-    int warps = 0;
-    fastk::choose_slots(static_cast<size_t>(f.slot_elems) * elem, fixed, fastk::bwd_shared_bytes(f), kSmemLimit, 8,
-                        f.nkinds, &bytes, &warps);
-    return static_cast<int64_t>(bytes);
+    r = fastk::choose_residency(static_cast<size_t>(f.slot_elems) * elem, fixed, fastk::bwd_shared_bytes(f), kSmemLimit,
+                                255, 2, std::min(fastk::kMaxSlots, 2 * f.nkinds));
   }
-  size_t bytes = 0;
-  int warps = 0;
-  const size_t shared = plan->dtype == LUNA_F64 ? fastk::ell_bytes<double>(f.m_total, f.m_terms)
-                                                : fastk::ell_bytes<float>(f.m_total, f.m_terms);
-  fastk::choose_stages(stage, fixed, shared, kSmemLimit, &bytes, &warps);
-  return static_cast<int64_t>(bytes);
+  return static_cast<int64_t>(r.block_bytes);
 }
 
 // Per-chunk partial rows of gy when the channels of a block are split over several warps.

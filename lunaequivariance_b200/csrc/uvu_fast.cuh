@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <type_traits>
 
 #include "plan.h"
@@ -162,6 +163,31 @@ __device__ __forceinline__ int64_t warp_lower_bound(const int* __restrict__ rowp
   const int64_t idx = lo + lane;
   const bool below = idx < hi && rowptr[idx] < bound;
   return lo + __popc(__ballot_sync(0xffffffffu, below));
+}
+
+// How a staged kernel is made resident: ring depth per warp, warps per CTA, CTAs per SM, dynamic shared memory.
+struct Residency {
+  int depth = 0;  // stages / slots per warp, 0 if nothing fits
+  int warps = 0;
+  int ctas = 0;
+  size_t block_bytes = 0;
+};
+// Picks the configuration with the most resident warps.  Registers are counted per SM sub-partition: a CTA's warps
+// are dealt round-robin to the four sub-partitions, each of which holds 16384 registers, so a CTA of w warps takes
+// ceil(w / 4) warp slots on the fullest one.  Ties go to the deeper ring (within [min_depth, max_depth]), then to
+// fewer CTAs.
+Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
+                           int regs_per_thread, int min_depth, int max_depth);
+// CTAs to launch: about `target` edges per warp, rounded up to whole waves of resident CTAs.
+int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count);
+
+// Target edges per warp when sizing the grid (tuning knob LUNA_B200_EPW).
+inline int64_t edges_per_warp(int64_t fallback) {
+  if (const char* knob = std::getenv("LUNA_B200_EPW")) {
+    const long long v = std::atoll(knob);
+    if (v > 0) return v;
+  }
+  return fallback;
 }
 
 // ---- per-edge coupling matrices -------------------------------------------------------------------------------------

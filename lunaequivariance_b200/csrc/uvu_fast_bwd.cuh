@@ -56,83 +56,151 @@ struct BwdParams {
 };
 
 // ---- arithmetic packets ---------------------------------------------------------------------------------------------
-// A lane's CPL channels are processed as NP packets of W channels: FP32 pairs (float2, packed FMAs) when CPL is even,
-// scalars otherwise.  Coupling-matrix entries are stored W times in shared memory so that one load fills a packet.
+// A lane's CPL channels are processed as NP packets of W channels: FP32 pairs with packed two-wide FMAs when CPL is
+// even, scalars otherwise.  Coupling-matrix entries are stored W times in shared memory so that one load fills a
+// packet.  A pair lives in one 64-bit register from the load to the last use (the packed instructions take 64-bit
+// operands; keeping the halves as separate floats costs a register move per operand).
+struct Pair {
+  unsigned long long v;
+};
 template <typename T, int CPL>
 struct Pk {
   using V = T;
   static constexpr int W = 1, NP = CPL;
 };
+#ifndef LUNA_BWD_PACKED
+#define LUNA_BWD_PACKED 0
+#endif
+#if LUNA_BWD_PACKED
 template <>
 struct Pk<float, 2> {
-  using V = float2;
+  using V = Pair;
   static constexpr int W = 2, NP = 1;
 };
 template <>
 struct Pk<float, 4> {
-  using V = float2;
+  using V = Pair;
   static constexpr int W = 2, NP = 2;
 };
-__device__ __forceinline__ float2 vfma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+#endif
+__device__ __forceinline__ Pair vfma(Pair a, Pair b, Pair c) {
+  Pair d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+  return d;
+}
+__device__ __forceinline__ Pair vmul(Pair a, Pair b) {
+  Pair d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
+  return d;
+}
+__device__ __forceinline__ Pair vadd(Pair a, Pair b) {
+  Pair d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
+  return d;
+}
+__device__ __forceinline__ Pair make_packet(const float* vals, Pair) {
+  Pair d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d.v) : "f"(vals[0]), "f"(vals[1]));
+  return d;
+}
+__device__ __forceinline__ void split_packet(Pair a, float* vals) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(vals[0]), "=f"(vals[1]) : "l"(a.v));
+}
+__device__ __forceinline__ float hsum(Pair a) {
+  float v[2];
+  split_packet(a, v);
+  return v[0] + v[1];
+}
 __device__ __forceinline__ float vfma(float a, float b, float c) { return fmaf(a, b, c); }
 __device__ __forceinline__ double vfma(double a, double b, double c) { return fma(a, b, c); }
-__device__ __forceinline__ float2 vmul(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float vmul(float a, float b) { return a * b; }
 __device__ __forceinline__ double vmul(double a, double b) { return a * b; }
-__device__ __forceinline__ float hsum(float2 a) { return a.x + a.y; }
 __device__ __forceinline__ float hsum(float a) { return a; }
 __device__ __forceinline__ double hsum(double a) { return a; }
-__device__ __forceinline__ void put(float2& v, int c, float x) {
-  if (c == 0)
-    v.x = x;
-  else
-    v.y = x;
+__device__ __forceinline__ float make_packet(const float* vals, float) { return vals[0]; }
+__device__ __forceinline__ double make_packet(const double* vals, double) { return vals[0]; }
+__device__ __forceinline__ void split_packet(float a, float* vals) { vals[0] = a; }
+__device__ __forceinline__ void split_packet(double a, double* vals) { vals[0] = a; }
+template <typename V>
+__device__ __forceinline__ V zero_packet() {
+  if constexpr (sizeof(V) == sizeof(Pair) && !std::is_floating_point<V>::value) {
+    return V{0ull};
+  } else {
+    return V(0);
+  }
 }
-__device__ __forceinline__ void put(float& v, int, float x) { v = x; }
-__device__ __forceinline__ void put(double& v, int, double x) { v = x; }
-__device__ __forceinline__ float get(float2 v, int c) { return c == 0 ? v.x : v.y; }
-__device__ __forceinline__ float get(float v, int) { return v; }
-__device__ __forceinline__ double get(double v, int) { return v; }
 
 // Memory row [channel][component] (CPL x D, this lane's channels) -> packets [component][packet].
 template <typename T, int CPL, int D>
 __device__ __forceinline__ void load_packets(const T* p, typename Pk<T, CPL>::V* out) {
+  using V = typename Pk<T, CPL>::V;
   constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
   T row[CPL * D];
   load_vectors<T, CPL, D>(p, row);
 #pragma unroll
-  for (int c = 0; c < CPL; ++c)
+  for (int i = 0; i < D; ++i)
 #pragma unroll
-    for (int i = 0; i < D; ++i) put(out[i * NP + c / W], c % W, row[c * D + i]);
+    for (int q = 0; q < NP; ++q) {
+      T vals[W];
+#pragma unroll
+      for (int c = 0; c < W; ++c) vals[c] = row[(q * W + c) * D + i];
+      out[i * NP + q] = make_packet(vals, V{});
+    }
 }
 template <typename T, int CPL, int D>
 __device__ __forceinline__ void unpack_packets(const typename Pk<T, CPL>::V* in, T* row) {
   constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
 #pragma unroll
-  for (int c = 0; c < CPL; ++c)
+  for (int i = 0; i < D; ++i)
 #pragma unroll
-    for (int i = 0; i < D; ++i) row[c * D + i] = get(in[i * NP + c / W], c % W);
+    for (int q = 0; q < NP; ++q) {
+      T vals[W];
+      split_packet(in[i * NP + q], vals);
+#pragma unroll
+      for (int c = 0; c < W; ++c) row[(q * W + c) * D + i] = vals[c];
+    }
+}
+
+// The lane's CPL consecutive channels of one component (already adjacent in memory) as packets.
+template <typename T, int CPL>
+__device__ __forceinline__ void load_lane_packets(const T* p, typename Pk<T, CPL>::V* out) {
+  if constexpr (Pk<T, CPL>::W == 2) {
+    if constexpr (CPL == 4) {
+      const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(p);
+      out[0].v = t.x;
+      out[1].v = t.y;
+    } else {
+      out[0].v = *reinterpret_cast<const unsigned long long*>(p);
+    }
+  } else {
+    load_vectors<T, CPL, 1>(p, out);
+  }
 }
 
 // One row of a coupling matrix (D3P entries, each stored W times) from shared memory; every lane reads the same
 // address, so each load is one broadcast.  Rows start on 16-byte boundaries except in FP32 without duplication (8).
 template <typename T, int W, int D3P, typename V>
 __device__ __forceinline__ void load_matrix_row(const T* p, V* row) {
-  constexpr int N = W * D3P;
-  constexpr int per = (W * sizeof(T) == 4 ? 8 : 16) / sizeof(T);
-  static_assert(N % per == 0, "row length must be a whole number of vectors");
-  T flat[N];
-  const Vec<T, per>* v = reinterpret_cast<const Vec<T, per>*>(p);
+  if constexpr (W == 2) {  // two packets per 128-bit load
+    static_assert(D3P % 2 == 0, "row length must be even");
+    const ulonglong2* v = reinterpret_cast<const ulonglong2*>(p);
 #pragma unroll
-  for (int n = 0; n < N / per; ++n) {
-    const Vec<T, per> t = v[n];
+    for (int n = 0; n < D3P / 2; ++n) {
+      const ulonglong2 t = v[n];
+      row[2 * n].v = t.x;
+      row[2 * n + 1].v = t.y;
+    }
+  } else {
+    constexpr int per = (sizeof(T) == 4 ? 8 : 16) / sizeof(T);
+    static_assert(D3P % per == 0, "row length must be a whole number of vectors");
+    const Vec<T, per>* v = reinterpret_cast<const Vec<T, per>*>(p);
 #pragma unroll
-    for (int c = 0; c < per; ++c) flat[n * per + c] = t.a[c];
+    for (int n = 0; n < D3P / per; ++n) {
+      const Vec<T, per> t = v[n];
+#pragma unroll
+      for (int c = 0; c < per; ++c) row[n * per + c] = t.a[c];
+    }
   }
-#pragma unroll
-  for (int k = 0; k < D3P; ++k)
-#pragma unroll
-    for (int c = 0; c < W; ++c) put(row[k], c, flat[k * W + c]);
 }
 
 // Adds the 32 lane contributions of tile rows [0, groups) and writes the entry pairs to gbuf[0 .. 2 * groups).
@@ -144,14 +212,14 @@ __device__ __noinline__ void flush_tile(const T* red, T* gbuf, int groups, int l
   if (lane < groups) {
     const T* row = red + lane * red_stride<T>();
     if constexpr (sizeof(T) == 4) {
-      float2 a0 = make_float2(0.f, 0.f), a1 = a0;
+      Pair a0{0ull}, a1{0ull};
 #pragma unroll
       for (int v = 0; v < 16; ++v) {
-        const float4 q = reinterpret_cast<const float4*>(row)[v];
-        a0 = __fadd2_rn(a0, make_float2(q.x, q.y));
-        a1 = __fadd2_rn(a1, make_float2(q.z, q.w));
+        const ulonglong2 q = reinterpret_cast<const ulonglong2*>(row)[v];
+        a0 = vadd(a0, Pair{q.x});
+        a1 = vadd(a1, Pair{q.y});
       }
-      reinterpret_cast<float2*>(gbuf)[lane] = __fadd2_rn(a0, a1);
+      reinterpret_cast<unsigned long long*>(gbuf)[lane] = vadd(a0, a1).v;
     } else {
       double s0 = 0.0, s1 = 0.0, t0 = 0.0, t1 = 0.0;
 #pragma unroll
@@ -175,13 +243,14 @@ __host__ __device__ inline size_t bwd_fixed_bytes(const FastMeta& f) {
                        static_cast<size_t>(kRedGroups) * red_stride<T>() + 32;
   return elems * sizeof(T) + kMaxSlots * sizeof(uint64_t);
 }
-// Per-CTA shared tables: the blob plus the w offsets of the paths.
+// Per-CTA shared tables: the blob plus one record per path.
 __host__ __device__ inline size_t bwd_shared_bytes(const FastMeta& f) {
-  return static_cast<size_t>(f.tb_bytes) + kMaxFastPaths * sizeof(int);
+  return static_cast<size_t>(f.tb_bytes) + kMaxFastPaths * sizeof(int4);
 }
 
-// WY: whether gy is produced (compiled in or out: the G work is half of the kernel).
-template <typename T, int CPL, int LX, int LO, bool WY>
+// WXW: whether gx and/or gw are produced; WY: whether gy is.  Compiled in or out: each is about half of the kernel,
+// and only the first needs the coupling matrices.
+template <typename T, int CPL, int LX, int LO, bool WXW, bool WY>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __grid_constant__ BwdParams<T> P) {
   using V = typename Pk<T, CPL>::V;
   constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
@@ -197,8 +266,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
   // CTA-wide tables
   for (int i = threadIdx.x; i < F.tb_bytes / 16; i += blockDim.x)
     reinterpret_cast<uint4*>(smem_raw)[i] = reinterpret_cast<const uint4*>(P.tables)[i];
-  int* wtab = reinterpret_cast<int*>(smem_raw + F.tb_bytes);  // global w offset of path q for this CTA's channels
-  for (int q = threadIdx.x; q < F.num_paths; q += blockDim.x) wtab[q] = F.w_goff[q] + c0;
+  // per path: offset of its w chunk in the unit, offset of its matrix, global w offset for this CTA's channels
+  int4* ptab = reinterpret_cast<int4*>(smem_raw + F.tb_bytes);
+  for (int q = threadIdx.x; q < F.num_paths; q += blockDim.x)
+    ptab[q] = make_int4(F.uw_soff[q], F.m_off[q], F.w_goff[q] + c0, 0);
   __syncthreads();
   const T* ell_c = reinterpret_cast<const T*>(smem_raw);
   const T* gy_c = reinterpret_cast<const T*>(smem_raw + F.tb_gyc);
@@ -229,7 +300,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
   const int64_t n_hi = gwarp == total_warps - 1 ? N : warp_lower_bound(P.src_rowptr, N, bound_hi, lane);
   if (n_lo >= n_hi) return;
   const int64_t p_begin = P.src_rowptr[n_lo], p_end = P.src_rowptr[n_hi];
-  const bool want_x = P.gx != nullptr, want_w = P.gw != nullptr;
+  const bool want_x = WXW && P.gx != nullptr, want_w = WXW && P.gw != nullptr;
   constexpr bool want_y = WY;
   const int64_t total_units = (p_end - p_begin) * nk;
 
@@ -242,7 +313,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
     __syncwarp();
     T* to = slots + static_cast<size_t>(s) * slot_elems;
     if (lane < np) {
-      bulk_copy_g2s(to + lane * chw, P.w + e * F.W + wtab[q0 + lane], static_cast<uint32_t>(chw * sizeof(T)), bar);
+      bulk_copy_g2s(to + lane * chw, P.w + e * F.W + ptab[q0 + lane].z, static_cast<uint32_t>(chw * sizeof(T)), bar);
     } else if (lane == np) {
       const int d3 = 2 * l3 + 1;
       bulk_copy_g2s(to + np * chw, P.g + d_node * F.O + F.o_off[l3] + c0 * d3,
@@ -281,16 +352,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
       });
     }
 #pragma unroll
-    for (int a = 0; a < XR; ++a) gxr[a] = V{};
+    for (int a = 0; a < XR; ++a) gxr[a] = zero_packet<V>();
 
 #pragma unroll 1
     for (; pos < pe && alive; ++pos) {
       // coupling matrices of this edge, computed while its first unit may still be in flight
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
-      compute_m_share<T, W == 2>(ell_c, ell_j, ybuf, mbuf, F.m_total, 0, 1, lane);
+      if constexpr (WXW) compute_m_share<T, W == 2>(ell_c, ell_j, ybuf, mbuf, F.m_total, 0, 1, lane);
       if (pos + 1 < p_end && lane < F.Y) y_next = P.y[static_cast<int64_t>(e1) * F.Y + lane];
       __syncwarp();
+      int tile_base = 0;  // first matrix entry held in the reduction tile
+      int tile_end = 0;   // one past the last entry written to the tile
 
       // one unit per output degree present; the per-degree arithmetic is selected by a switch so that the wait and
       // the refill exist once in the loop
@@ -300,9 +373,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
         constexpr int d3p = d3 + 1;
         V g2[d3 * NP];
         load_packets<T, CPL, d3>(unit + F.ug_soff[l3] + lane * (CPL * d3), g2);
-        const int q_first = F.pair_ptr[l3 * L1S];
-        int tile_base = F.m_off[q_first];  // first matrix entry held in the reduction tile
-        int tile_end = tile_base;          // one past the last entry written to the tile
         static_for<0, LX + 1>([&](auto l1c) {
           constexpr int l1 = decltype(l1c)::value;
           constexpr int d1 = 2 * l1 + 1;
@@ -310,44 +380,45 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
           const int q_end = F.pair_ptr[l3 * L1S + l1 + 1];
 #pragma unroll 1
           for (int q = F.pair_ptr[l3 * L1S + l1]; q < q_end; ++q) {
-            const int m_off = F.m_off[q];
-            V w2[NP];
-            load_packets<T, CPL, 1>(unit + F.uw_soff[q] + lane * CPL, w2);
+            const int4 rec = ptab[q];
+            const int m_off = rec.y;
+            V w2[NP];  // a lane's consecutive channels are already adjacent in memory
+            load_lane_packets<T, CPL>(unit + rec.x + lane * CPL, w2);
             const V* xl = &xr[l1 * l1 * NP];
             V* gxl = &gxr[l1 * l1 * NP];
-            V wg[d3 * NP];
-            if (want_y) {
-#pragma unroll
-              for (int a = 0; a < d3 * NP; ++a) wg[a] = vmul(w2[a % NP], g2[a]);
-              if (m_off + span - tile_base > 2 * kRedGroups) {  // tile full: reduce what it holds
-                flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
-                tile_base = m_off;
-              }
+            if (want_y && m_off + span - tile_base > 2 * kRedGroups) {  // tile full: reduce what it holds
+              flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
+              tile_base = m_off;
             }
             T* tile = red + ((m_off - tile_base) / 2) * red_stride<T>() + lane * 2;
             V dot[NP];
 #pragma unroll
-            for (int p = 0; p < NP; ++p) dot[p] = V{};
+            for (int p = 0; p < NP; ++p) dot[p] = zero_packet<V>();
             const T* mrows = mbuf + W * m_off;
 #pragma unroll
             for (int i = 0; i < d1; ++i) {
-              V mrow[d3p];
-              load_matrix_row<T, W, d3p, V>(mrows + i * (W * d3p), mrow);
+              if constexpr (WXW) {
+                V mrow[d3p];
+                load_matrix_row<T, W, d3p, V>(mrows + i * (W * d3p), mrow);
 #pragma unroll
-              for (int p = 0; p < NP; ++p) {
-                V sv = vmul(mrow[0], g2[p]);
+                for (int p = 0; p < NP; ++p) {
+                  V sv = vmul(mrow[0], g2[p]);
 #pragma unroll
-                for (int k = 1; k < d3; ++k) sv = vfma(mrow[k], g2[k * NP + p], sv);
-                gxl[i * NP + p] = vfma(w2[p], sv, gxl[i * NP + p]);
-                dot[p] = vfma(xl[i * NP + p], sv, dot[p]);
+                  for (int k = 1; k < d3; ++k) sv = vfma(mrow[k], g2[k * NP + p], sv);
+                  gxl[i * NP + p] = vfma(w2[p], sv, gxl[i * NP + p]);
+                  dot[p] = vfma(xl[i * NP + p], sv, dot[p]);
+                }
               }
               if (want_y) {
+                V xw[NP];
+#pragma unroll
+                for (int p = 0; p < NP; ++p) xw[p] = vmul(xl[i * NP + p], w2[p]);
                 T grow[d3p];
 #pragma unroll
                 for (int k = 0; k < d3; ++k) {
-                  V acc = vmul(xl[i * NP], wg[k * NP]);
+                  V acc = vmul(xw[0], g2[k * NP]);
 #pragma unroll
-                  for (int p = 1; p < NP; ++p) acc = vfma(xl[i * NP + p], wg[k * NP + p], acc);
+                  for (int p = 1; p < NP; ++p) acc = vfma(xw[p], g2[k * NP + p], acc);
                   grow[k] = hsum(acc);
                 }
                 grow[d3] = T(0);
@@ -362,7 +433,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
             if (want_w) {
               T gwv[CPL];
               unpack_packets<T, CPL, 1>(dot, gwv);
-              T* dstw = P.gw + static_cast<int64_t>(e0) * F.W + F.w_goff[q] + c0 + lane * CPL;
+              T* dstw = P.gw + static_cast<int64_t>(e0) * F.W + rec.z + lane * CPL;
               if (P.acc_w) {
                 T old[CPL];
                 load_vectors<T, CPL, 1>(dstw, old);
@@ -373,7 +444,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
             }
           }
         });
-        if (want_y && tile_end > tile_base) flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
       };
 #pragma unroll 1
       for (int kind = 0; kind < nk; ++kind) {
@@ -419,6 +489,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
       if (!alive) break;
 
       if (want_y) {
+        if (tile_end > tile_base) flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
         // gy[e, j] = sum_t c[t] * G[m[t]]; two lanes share a j when the row is short enough
         const int lpj = F.Y <= 16 ? 2 : 1;
         const int j = lpj == 2 ? lane >> 1 : lane, h = lpj == 2 ? lane & 1 : 0;
@@ -489,10 +560,6 @@ __global__ void reduce_gy_partial(const T* __restrict__ partial, T* __restrict__
   gy[idx] = acc;
 }
 
-// Picks ring slots per warp and warps per CTA: as many resident warps as registers and shared memory allow, each
-// with at least one whole edge (nkinds units) and at most two in its ring.  Returns the slot count, 0 if nothing fits.
-int choose_slots(size_t slot_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin, int max_warps_by_regs,
-                 int nkinds, size_t* block_bytes, int* warps);
 
 template <typename T, int CPL, int LX, int LO>
 int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
@@ -528,20 +595,25 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     if (!aligned_to(scratch, 16)) return fail(LUNA_ERR_MISALIGNED, "scratch must be 16-byte aligned");
     P.gy_partial = static_cast<T*>(scratch);
   }
-  auto kernel = gy != nullptr ? fast_bwd_kernel<T, CPL, LX, LO, true> : fast_bwd_kernel<T, CPL, LX, LO, false>;
+  if (gx == nullptr && gy == nullptr && gw == nullptr) return LUNA_OK;
+  const bool wxw = gx != nullptr || gw != nullptr;
+  auto kernel = gy == nullptr ? fast_bwd_kernel<T, CPL, LX, LO, true, false>
+                              : (wxw ? fast_bwd_kernel<T, CPL, LX, LO, true, true>
+                                     : fast_bwd_kernel<T, CPL, LX, LO, false, true>);
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
-  const int regs_per_warp = (std::max(attr.numRegs, 1) * 32 + 511) / 512 * 512;
-  size_t block_bytes = 0;
-  int nwarps = kWarps;
-  P.slots = choose_slots(static_cast<size_t>(f.slot_elems) * sizeof(T), bwd_fixed_bytes<T, CPL>(f), bwd_shared_bytes(f),
-                         dt.max_smem_optin, 65536 / regs_per_warp, f.nkinds, &block_bytes, &nwarps);
-  if (P.slots == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
+  // between two units and two edges in a warp's ring
+  const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), bwd_fixed_bytes<T, CPL>(f),
+                                       bwd_shared_bytes(f), dt.max_smem_optin, attr.numRegs, 2,
+                                       std::min(kMaxSlots, 2 * f.nkinds));
+  if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
+  P.slots = r.depth;
+  const size_t block_bytes = r.block_bytes;
+  const int nwarps = r.warps;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
-  int64_t warps = std::max<int64_t>(1, ceil_div(graph->num_edges, 256));
-  int64_t blocks = ceil_div(warps, nwarps);
-  const int64_t wave = static_cast<int64_t>(dt.sm_count) * std::max<int64_t>(1, dt.max_smem_optin / std::max<size_t>(block_bytes, 1));
-  if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
+  // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
+  LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
   kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged backward");

@@ -239,9 +239,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_fwd_kernel(const __gri
   }
 }
 
-// Host side: picks the stage count, sets the shared-memory attribute, launches.
-int choose_stages(size_t stage_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
-                  size_t* block_bytes, int* warps);
 
 template <typename T, int CPL, int LX, int LO>
 int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
@@ -262,18 +259,19 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.num_edges = graph->num_edges;
   P.accumulate = accumulate ? 1 : 0;
   const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
-  size_t block_bytes = 0;
-  int nwarps = kWarps;
-  P.stages = choose_stages(stage, fwd_fixed_bytes<T, CPL>(f), ell_bytes<T>(f.m_total, f.m_terms), dt.max_smem_optin,
-                           &block_bytes, &nwarps);
-  if (P.stages == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged forward needs more shared memory than the device has");
   auto kernel = fast_fwd_kernel<T, CPL, LX, LO>;
+  cudaFuncAttributes attr;
+  LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
+  const Residency r = choose_residency(stage, fwd_fixed_bytes<T, CPL>(f), ell_bytes<T>(f.m_total, f.m_terms),
+                                       dt.max_smem_optin, attr.numRegs, 2, 3);
+  if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged forward needs more shared memory than the device has");
+  P.stages = r.depth;
+  const size_t block_bytes = r.block_bytes;
+  const int nwarps = r.warps;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
-  // about 512 edges per warp, rounded to whole waves of resident CTAs
-  int64_t warps = std::max<int64_t>(1, ceil_div(graph->num_edges, 512));
-  int64_t blocks = ceil_div(warps, nwarps);
-  const int64_t wave = static_cast<int64_t>(dt.sm_count) * std::max<int64_t>(1, dt.max_smem_optin / std::max<size_t>(block_bytes, 1));
-  if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
+  // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
+  LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
   kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged forward");
