@@ -8,22 +8,30 @@ namespace luna {
 namespace fastk {
 
 Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
-                           int regs_per_thread, int min_depth, int max_depth) {
+                           int regs_per_thread, int max_warps, int min_depth, int max_depth) {
   int max_ctas = 4;
   if (const char* knob = std::getenv("LUNA_B200_MAX_CTAS")) max_ctas = std::max(1, std::atoi(knob));
   if (const char* knob = std::getenv("LUNA_B200_DEPTH")) max_depth = std::max(min_depth, std::min(max_depth, std::atoi(knob)));
+  if (const char* knob = std::getenv("LUNA_B200_MAXW")) max_warps = std::max(1, std::min(max_warps, std::atoi(knob)));
+  if (const char* knob = std::getenv("LUNA_B200_MIN_DEPTH")) min_depth = std::max(min_depth, std::min(max_depth, std::atoi(knob)));
   const int regs_per_warp = (std::max(regs_per_thread, 1) + 7) / 8 * 8 * 32;
   const int warp_slots = std::max(1, 16384 / regs_per_warp);  // per sub-partition
   Residency best;
   int best_score = 0;
   for (int ctas = 1; ctas <= max_ctas; ++ctas) {
     const size_t budget = static_cast<size_t>(max_smem_optin + 1024) / ctas - 1024;  // 1 KB reserved per CTA
-    for (int w = 1; w <= kMaxWarps; ++w) {
+    for (int w = 1; w <= std::min(max_warps, kMaxWarps); ++w) {
       if (ctas * ((w + 3) / 4) > warp_slots) continue;
       for (int depth = min_depth; depth <= max_depth; ++depth) {
         const size_t bytes = shared_bytes + w * (depth * ring_bytes + fixed_bytes);
         if (bytes > budget) continue;
-        const int score = w * ctas * 64 + (depth - min_depth) * 4 + (max_ctas - ctas);
+        // issue-rate model: a sub-partition with n resident warps runs at n / (n + 2) of its peak
+        int score = 0;
+        for (int part = 0; part < 4; ++part) {
+          const int n = ctas * (w / 4 + (part < w % 4 ? 1 : 0));
+          score += 4096 * n / (n + 2);
+        }
+        score = score * 16 + (depth - min_depth) * 4 + (max_ctas - ctas);
         if (score > best_score) {
           best_score = score;
           best.depth = depth;
@@ -84,7 +92,7 @@ int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which) {
     const size_t shared = plan->dtype == LUNA_F64 ? fastk::ell_bytes<double>(f.m_total, f.m_terms)
                                                   : fastk::ell_bytes<float>(f.m_total, f.m_terms);
     r = fastk::choose_residency(static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * elem, fixed, shared, kSmemLimit,
-                                255, 2, 3);
+                                255, fastk::kFwdMaxWarps, 2, 3);
   } else {
     if (plan->dtype == LUNA_F64)
       fixed = f.cpl == 2 ? fastk::bwd_fixed_bytes<double, 2>(f) : fastk::bwd_fixed_bytes<double, 1>(f);
@@ -92,7 +100,7 @@ int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which) {
       fixed = f.cpl == 4 ? fastk::bwd_fixed_bytes<float, 4>(f)
                          : (f.cpl == 2 ? fastk::bwd_fixed_bytes<float, 2>(f) : fastk::bwd_fixed_bytes<float, 1>(f));
     r = fastk::choose_residency(static_cast<size_t>(f.slot_elems) * elem, fixed, fastk::bwd_shared_bytes(f), kSmemLimit,
-                                255, 2, std::min(fastk::kMaxSlots, 2 * f.nkinds));
+                                255, 8, 2, std::min(fastk::kMaxSlots, 2 * f.nkinds));
   }
   return static_cast<int64_t>(r.block_bytes);
 }

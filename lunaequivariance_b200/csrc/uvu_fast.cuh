@@ -25,7 +25,8 @@ namespace luna {
 namespace fastk {
 
 constexpr int kWarps = 4;           // default warps per CTA; each warp streams its own edge range
-constexpr int kMaxWarps = 8;        // upper bound when shared memory allows only one CTA per SM
+constexpr int kMaxWarps = 16;       // upper bound on warps per CTA
+constexpr int kFwdMaxWarps = 8;     // forward kernel: its launch bounds leave it 255 registers
 constexpr int kMaxStages = 4;
 constexpr uint32_t kWaitLimit = 1u << 20;   // bounded mbarrier polling: tries per wait
 
@@ -177,7 +178,7 @@ struct Residency {
 // ceil(w / 4) warp slots on the fullest one.  Ties go to the deeper ring (within [min_depth, max_depth]), then to
 // fewer CTAs.
 Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
-                           int regs_per_thread, int min_depth, int max_depth);
+                           int regs_per_thread, int max_warps, int min_depth, int max_depth);
 // CTAs to launch: about `target` edges per warp, rounded up to whole waves of resident CTAs.
 int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count);
 

@@ -25,7 +25,7 @@ namespace luna {
 namespace fastk {
 
 constexpr int kMaxSlots = 8;    // ring slots per warp
-constexpr int kRedGroups = 32;  // rows of the reduction tile: one entry pair each, one row per lane at flush time
+constexpr int kRedGroups = 16;  // rows of the reduction tile: one entry pair each, two lanes per row at flush time
 
 // Elements per tile row: 32 lanes x 2 entries plus 16 bytes, so that lanes reading different rows with 128-bit loads
 // hit different banks.
@@ -204,34 +204,46 @@ __device__ __forceinline__ void load_matrix_row(const T* p, V* row) {
 }
 
 // Adds the 32 lane contributions of tile rows [0, groups) and writes the entry pairs to gbuf[0 .. 2 * groups).
-// Called from many places of the unrolled kernel, so it stays a real function: the hot loop has to fit the
-// instruction cache.
+// Lanes L and L + 16 share row L: each adds one half of the contributions, a shuffle joins the halves.  Called from
+// many places of the unrolled kernel, so it stays a real function: the hot loop has to fit the instruction cache.
 template <typename T>
 __device__ __noinline__ void flush_tile(const T* red, T* gbuf, int groups, int lane) {
   __syncwarp();
-  if (lane < groups) {
-    const T* row = red + lane * red_stride<T>();
-    if constexpr (sizeof(T) == 4) {
-      Pair a0{0ull}, a1{0ull};
+  const int r = lane & 15, half = lane >> 4;
+  const T* row = red + r * red_stride<T>() + half * 32;
+  T s0, s1;
+  if constexpr (sizeof(T) == 4) {
+    Pair a0{0ull}, a1{0ull};
 #pragma unroll
-      for (int v = 0; v < 16; ++v) {
-        const ulonglong2 q = reinterpret_cast<const ulonglong2*>(row)[v];
-        a0 = vadd(a0, Pair{q.x});
-        a1 = vadd(a1, Pair{q.y});
-      }
-      reinterpret_cast<unsigned long long*>(gbuf)[lane] = vadd(a0, a1).v;
-    } else {
-      double s0 = 0.0, s1 = 0.0, t0 = 0.0, t1 = 0.0;
-#pragma unroll
-      for (int v = 0; v < 32; v += 2) {
-        const double2 p = reinterpret_cast<const double2*>(row)[v], q = reinterpret_cast<const double2*>(row)[v + 1];
-        s0 += p.x;
-        s1 += p.y;
-        t0 += q.x;
-        t1 += q.y;
-      }
-      reinterpret_cast<double2*>(gbuf)[lane] = make_double2(s0 + t0, s1 + t1);
+    for (int v = 0; v < 8; ++v) {
+      const ulonglong2 q = reinterpret_cast<const ulonglong2*>(row)[v];
+      a0 = vadd(a0, Pair{q.x});
+      a1 = vadd(a1, Pair{q.y});
     }
+    float both[2];
+    split_packet(vadd(a0, a1), both);
+    s0 = both[0];
+    s1 = both[1];
+  } else {
+    double t0 = 0.0, t1 = 0.0;
+    s0 = 0.0;
+    s1 = 0.0;
+#pragma unroll
+    for (int v = 0; v < 16; v += 2) {
+      const double2 p = reinterpret_cast<const double2*>(row)[v], q = reinterpret_cast<const double2*>(row)[v + 1];
+      s0 += p.x;
+      s1 += p.y;
+      t0 += q.x;
+      t1 += q.y;
+    }
+    s0 += t0;
+    s1 += t1;
+  }
+  s0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+  s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+  if (lane < groups) {
+    Vec<T, 2> pr{{s0, s1}};
+    reinterpret_cast<Vec<T, 2>*>(gbuf)[lane] = pr;
   }
   __syncwarp();
 }
@@ -250,8 +262,9 @@ __host__ __device__ inline size_t bwd_shared_bytes(const FastMeta& f) {
 
 // WXW: whether gx and/or gw are produced; WY: whether gy is.  Compiled in or out: each is about half of the kernel,
 // and only the first needs the coupling matrices.
-template <typename T, int CPL, int LX, int LO, bool WXW, bool WY>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __grid_constant__ BwdParams<T> P) {
+// MAXW warps per CTA at most and MINB CTAs per SM at least: together they cap the registers per thread.
+template <typename T, int CPL, int LX, int LO, bool WXW, bool WY, int MAXW, int MINB>
+__global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_constant__ BwdParams<T> P) {
   using V = typename Pk<T, CPL>::V;
   constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
   constexpr int L1S = kMaxFastL + 1;
@@ -376,7 +389,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
         static_for<0, LX + 1>([&](auto l1c) {
           constexpr int l1 = decltype(l1c)::value;
           constexpr int d1 = 2 * l1 + 1;
-          constexpr int span = (d1 * d3p + 3) / 4 * 4;  // entries the matrix occupies
           const int q_end = F.pair_ptr[l3 * L1S + l1 + 1];
 #pragma unroll 1
           for (int q = F.pair_ptr[l3 * L1S + l1]; q < q_end; ++q) {
@@ -386,17 +398,26 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
             load_lane_packets<T, CPL>(unit + rec.x + lane * CPL, w2);
             const V* xl = &xr[l1 * l1 * NP];
             V* gxl = &gxr[l1 * l1 * NP];
-            if (want_y && m_off + span - tile_base > 2 * kRedGroups) {  // tile full: reduce what it holds
-              flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
-              tile_base = m_off;
-            }
-            T* tile = red + ((m_off - tile_base) / 2) * red_stride<T>() + lane * 2;
+            // rows go to the tile in chunks that fit it; a chunk that does not fit behind what the tile holds
+            // first reduces that
+            constexpr int rows_per_chunk = (2 * kRedGroups) / d3p < d1 ? (2 * kRedGroups) / d3p : d1;
+            T* tile = nullptr;
             V dot[NP];
 #pragma unroll
             for (int p = 0; p < NP; ++p) dot[p] = zero_packet<V>();
             const T* mrows = mbuf + W * m_off;
 #pragma unroll
             for (int i = 0; i < d1; ++i) {
+              if (want_y && i % rows_per_chunk == 0) {
+                const int chunk_rows = d1 - i < rows_per_chunk ? d1 - i : rows_per_chunk;
+                const int first = m_off + i * d3p;
+                if (first + chunk_rows * d3p - tile_base > 2 * kRedGroups) {
+                  flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
+                  tile_base = first;
+                }
+                tile = red + ((first - tile_base) / 2) * red_stride<T>() + lane * 2;
+                tile_end = first + chunk_rows * d3p;
+              }
               if constexpr (WXW) {
                 V mrow[d3p];
                 load_matrix_row<T, W, d3p, V>(mrows + i * (W * d3p), mrow);
@@ -425,11 +446,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_bwd_kernel(const __gri
 #pragma unroll
                 for (int kk = 0; kk < d3p / 2; ++kk) {
                   Vec<T, 2> pr{{grow[2 * kk], grow[2 * kk + 1]}};
-                  *reinterpret_cast<Vec<T, 2>*>(tile + (i * (d3p / 2) + kk) * red_stride<T>()) = pr;
+                  *reinterpret_cast<Vec<T, 2>*>(tile + ((i % rows_per_chunk) * (d3p / 2) + kk) * red_stride<T>()) = pr;
                 }
               }
             }
-            if (want_y) tile_end = m_off + d1 * d3p;
             if (want_w) {
               T gwv[CPL];
               unpack_packets<T, CPL, 1>(dot, gwv);
@@ -597,14 +617,18 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   }
   if (gx == nullptr && gy == nullptr && gw == nullptr) return LUNA_OK;
   const bool wxw = gx != nullptr || gw != nullptr;
-  auto kernel = gy == nullptr ? fast_bwd_kernel<T, CPL, LX, LO, true, false>
-                              : (wxw ? fast_bwd_kernel<T, CPL, LX, LO, true, true>
-                                     : fast_bwd_kernel<T, CPL, LX, LO, false, true>);
+  // Register budget by shape, through the launch bounds: FP32 with four channels per lane or degree-3 blocks runs up
+  // to 12 warps in a CTA (168 registers), smaller FP32 shapes up to 16 (128 registers); FP64 keeps 8 warps (255).
+  constexpr int MAXW = sizeof(T) == 8 ? 8 : ((CPL == 4 || LX == 3 || LO == 3) ? 12 : 16);
+  constexpr int MINB = 1;
+  auto kernel = gy == nullptr ? fast_bwd_kernel<T, CPL, LX, LO, true, false, MAXW, MINB>
+                              : (wxw ? fast_bwd_kernel<T, CPL, LX, LO, true, true, MAXW, MINB>
+                                     : fast_bwd_kernel<T, CPL, LX, LO, false, true, MAXW, MINB>);
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
   // between two units and two edges in a warp's ring
   const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), bwd_fixed_bytes<T, CPL>(f),
-                                       bwd_shared_bytes(f), dt.max_smem_optin, attr.numRegs, 2,
+                                       bwd_shared_bytes(f), dt.max_smem_optin, attr.numRegs, MAXW, 2,
                                        std::min(kMaxSlots, 2 * f.nkinds));
   if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
   P.slots = r.depth;

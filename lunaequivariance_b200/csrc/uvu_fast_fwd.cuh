@@ -45,7 +45,7 @@ __host__ __device__ inline size_t fwd_fixed_bytes(const FastMeta& f) {
 }
 
 template <typename T, int CPL, int LX, int LO>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) fast_fwd_kernel(const __grid_constant__ FwdParams<T> P) {
+__global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __grid_constant__ FwdParams<T> P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr bool kPairs = UsePairs<T, CPL>::value;
   constexpr int NP = CPL / 2;  // channel pairs per lane (packed path)
@@ -263,7 +263,7 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
   const Residency r = choose_residency(stage, fwd_fixed_bytes<T, CPL>(f), ell_bytes<T>(f.m_total, f.m_terms),
-                                       dt.max_smem_optin, attr.numRegs, 2, 3);
+                                       dt.max_smem_optin, attr.numRegs, kFwdMaxWarps, 2, 3);
   if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged forward needs more shared memory than the device has");
   P.stages = r.depth;
   const size_t block_bytes = r.block_bytes;
