@@ -125,6 +125,26 @@ LUNA_API int luna_uvu_conv_bwd(luna_uvu_plan* plan, const luna_graph* graph, con
                       const void* g, void* gx, void* gy, void* gw, void* scratch, int64_t scratch_bytes,
                       void* stream);
 
+/* Same result as luna_uvu_conv_bwd, for callers that cannot allocate device memory and so have no scratch
+ * buffer to pass: code running inside another program's step without an allocator of its own, loops that must
+ * not hit cudaMalloc's device-wide synchronisation, processes whose memory pool is fixed at start-up.  No
+ * counterpart in the reference (its operators allocate through torch).  The partial rows that luna_uvu_conv_bwd
+ * keeps in caller scratch live in an array built into the library instead:
+ *   - the array is luna_uvu_conv_noalloc_max_scratch_bytes() = 8 MiB and occupies that much memory on every GPU
+ *     that loads the library, until the process exits;
+ *   - a graph for which luna_uvu_conv_scratch_bytes exceeds it is refused with LUNA_ERR_SCRATCH;
+ *   - the call itself performs no cudaMalloc/cudaFree.  The plan's tables must therefore already be on the
+ *     current device (any earlier call with the plan there, e.g. luna_uvu_check_status, uploads them); if they
+ *     are not, LUNA_ERR_INVALID_ARGUMENT is returned instead of allocating;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first
+ *     call before starting any stream capture;
+ *   - every call on a device uses the same array, which still holds the previous call's partial rows (the kernel
+ *     overwrites all rows it reads, nothing needs clearing).  Calls that overlap on one GPU race on it: issue them
+ *     in stream order. */
+LUNA_API int64_t luna_uvu_conv_noalloc_max_scratch_bytes(void);
+LUNA_API int luna_uvu_conv_bwd_noalloc(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,
+                              const void* w, const void* g, void* gx, void* gy, void* gw, void* stream);
+
 /* Second derivatives.  rx, ry, rw are the cotangents of (gx, gy, gw); any may be null (= zero, never
  * materialised).  hx, hy, hw, hg receive d/d(x, y, w, g) of <rx,gx>+<ry,gy>+<rw,gw>; a null output is skipped.
  * Replaces double_backward.run (src/lunatp/uvu_conv/kernels/double_backward.py:1635-1800). */
