@@ -14,7 +14,8 @@ import threading
 import torch
 
 _PACKAGE_DIR = os.path.dirname(os.path.abspath(__file__))
-LIBRARY_PATH = os.path.join(_PACKAGE_DIR, "_lib", "libluna_b200.so")
+# LUNA_B200_LIBRARY selects another build of the same library (kernel tuning experiments).
+LIBRARY_PATH = os.environ.get("LUNA_B200_LIBRARY") or os.path.join(_PACKAGE_DIR, "_lib", "libluna_b200.so")
 
 LUNA_OK = 0
 LUNA_ERR_INVALID_ARGUMENT = -1

@@ -1,6 +1,7 @@
 // Plan creation: validates a path description, builds the lookup tables of the table-driven kernels and, when the
 // configuration allows it, the metadata of the staged (bulk-copy) kernels; uploads tables once per device.
 #include "plan.h"
+#include "uvu_fast.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -175,6 +176,26 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl) {
   m_ptr.push_back(static_cast<int>(m_j.size()));
   f.m_total = total;
   if (total > kMaxMEntries) return false;
+
+  // canonical full path list?  (all degrees 0..LX / 0..LO present, every allowed triple exactly once, weight
+  // blocks in (l1, l2, l3) order)
+  f.canon_l2 = -1;
+  {
+    int L2 = 0;
+    for (const auto& p : paths) L2 = std::max(L2, (p.d2 - 1) / 2);
+    bool canon = f.chunks >= 1 && fastk::canon_wrank(f.LX, L2, f.LO, -1, -1, -1) == static_cast<int>(paths.size()) &&
+                 fastk::canon_moff(f.LX, L2, f.LO, -1, -1, -1) == total;
+    for (int l = 0; l <= f.LX && canon; ++l) canon = f.x_off[l] >= 0 && f.xs_off[l] == chw * l * l;
+    for (int l = 0; l <= f.LO && canon; ++l) canon = f.o_off[l] >= 0;
+    for (size_t q = 0; q < order.size() && canon; ++q) {
+      const PathRec& p = paths[order[q]];
+      const int l1 = (p.d1 - 1) / 2, l2 = (p.d2 - 1) / 2, l3 = (p.d3 - 1) / 2;
+      canon = (p.d1 % 2 == 1) && (p.d2 % 2 == 1) && (p.d3 % 2 == 1) && fastk::canon_ok(f.LX, L2, f.LO, l1, l2, l3) &&
+              f.w_soff[q] == fastk::canon_wrank(f.LX, L2, f.LO, l1, l2, l3) * chw &&
+              f.m_off[q] == fastk::canon_moff(f.LX, L2, f.LO, l1, l2, l3);
+    }
+    if (canon) f.canon_l2 = L2;
+  }
 
   // the program in padded (ELL) form for the kernels: term t of entry m at [t * m_total + m], exactly two
   // (zero-padded) terms per entry, which is enough for l <= 3

@@ -64,6 +64,7 @@ struct CopyPiece {
 // entries are zero).
 struct FastMeta {
   int LX, LO;                 // highest degree present in x / out
+  int canon_l2;               // highest edge-harmonic degree if the path list is the canonical full list, else -1
   int cpl;                    // channels per lane
   int chunks;                 // channel chunks per feature block (a warp handles 32 * cpl channels)
   int ch;                     // channels per block (uniform)

@@ -46,9 +46,12 @@ Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_
 }
 
 int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count) {
-  const int64_t warps = std::max<int64_t>(1, ceil_div(num_edges, edges_per_warp(target)));
-  int64_t blocks = ceil_div(warps, r.warps);
+  // A small graph still fills one wave: fewer edges per warp (not below 48) rather than idle SMs.
   const int64_t wave = static_cast<int64_t>(sm_count) * r.ctas;
+  const int64_t fill = num_edges / std::max<int64_t>(1, wave * r.warps);
+  const int64_t per_warp = std::max<int64_t>(48, std::min<int64_t>(edges_per_warp(target), fill));
+  const int64_t warps = std::max<int64_t>(1, ceil_div(num_edges, per_warp));
+  int64_t blocks = ceil_div(warps, r.warps);
   if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
   return blocks;
 }

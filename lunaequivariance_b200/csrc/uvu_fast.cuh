@@ -191,6 +191,44 @@ inline int64_t edges_per_warp(int64_t fallback) {
   return fallback;
 }
 
+// ---- canonical path lists ---------------------------------------------------------------------------------------
+// Most models couple every degree of x with every degree of the edge harmonics into every degree of the output:
+// all (l1, l2, l3) with l1 <= LX, l2 <= L2, l3 <= LO that satisfy the triangle rule and have an even degree sum,
+// listed in (l1, l2, l3) order, which is also the order of their weight blocks.  For such a list everything the
+// inner loops need (which paths exist, where a path's weights sit in a stage, where its coupling matrix sits in
+// the per-edge buffer) is known at compile time, so the loops over paths unroll completely and the compiler can
+// move shared-memory loads ahead of the arithmetic of the previous path.  These functions define the list; the
+// plan checks a configuration against them (FastMeta::canon_l2) and the kernels use them as constants.
+__host__ __device__ constexpr bool canon_ok(int LX, int L2, int LO, int l1, int l2, int l3) {
+  const int lo = l1 > l2 ? l1 - l2 : l2 - l1;
+  return l1 <= LX && l2 <= L2 && l3 <= LO && l3 >= lo && l3 <= l1 + l2 && ((l1 + l2 + l3) % 2 == 0);
+}
+// position of the path's weight block among the weight blocks
+__host__ __device__ constexpr int canon_wrank(int LX, int L2, int LO, int a, int b, int c) {
+  int r = 0;
+  for (int l1 = 0; l1 <= LX; ++l1)
+    for (int l2 = 0; l2 <= L2; ++l2)
+      for (int l3 = 0; l3 <= LO; ++l3) {
+        if (l1 == a && l2 == b && l3 == c) return r;
+        if (canon_ok(LX, L2, LO, l1, l2, l3)) ++r;
+      }
+  return r;  // (a, b, c) past the end: the number of paths
+}
+// first entry of the path's coupling matrix in the per-edge buffer: matrices in (l3, l1, l2) order, rows of
+// d3 + 1 entries, every matrix padded to a multiple of four entries; past-the-end arguments give the total
+__host__ __device__ constexpr int canon_moff(int LX, int L2, int LO, int a, int b, int c) {
+  int m = 0;
+  for (int l3 = 0; l3 <= LO; ++l3)
+    for (int l1 = 0; l1 <= LX; ++l1)
+      for (int l2 = 0; l2 <= L2; ++l2) {
+        if (!canon_ok(LX, L2, LO, l1, l2, l3)) continue;
+        if (l1 == a && l2 == b && l3 == c) return m;
+        m += (2 * l1 + 1) * (2 * l3 + 2);
+        while (m % 4) ++m;
+      }
+  return m;
+}
+
 // ---- per-edge coupling matrices -------------------------------------------------------------------------------------
 // The program that turns an edge's y row into the M matrices lives in shared memory in padded form: term t of
 // entry m is (ell_c[t * m_total + m], ell_j[t * m_total + m]); padding terms have coefficient 0.

@@ -19,7 +19,7 @@
 
 #include <algorithm>
 
-#include "uvu_fast.cuh"
+#include "uvu_packets.cuh"
 
 namespace luna {
 namespace fastk {
@@ -55,153 +55,12 @@ struct BwdParams {
   int acc_x, acc_y, acc_w;
 };
 
-// ---- arithmetic packets ---------------------------------------------------------------------------------------------
-// A lane's CPL channels are processed as NP packets of W channels: FP32 pairs with packed two-wide FMAs when CPL is
-// even, scalars otherwise.  Coupling-matrix entries are stored W times in shared memory so that one load fills a
-// packet.  A pair lives in one 64-bit register from the load to the last use (the packed instructions take 64-bit
-// operands; keeping the halves as separate floats costs a register move per operand).
-struct Pair {
-  unsigned long long v;
-};
-template <typename T, int CPL>
-struct Pk {
-  using V = T;
-  static constexpr int W = 1, NP = CPL;
-};
 #ifndef LUNA_BWD_PACKED
 #define LUNA_BWD_PACKED 0
 #endif
-#if LUNA_BWD_PACKED
-template <>
-struct Pk<float, 2> {
-  using V = Pair;
-  static constexpr int W = 2, NP = 1;
-};
-template <>
-struct Pk<float, 4> {
-  using V = Pair;
-  static constexpr int W = 2, NP = 2;
-};
-#endif
-__device__ __forceinline__ Pair vfma(Pair a, Pair b, Pair c) {
-  Pair d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.v) : "l"(a.v), "l"(b.v), "l"(c.v));
-  return d;
-}
-__device__ __forceinline__ Pair vmul(Pair a, Pair b) {
-  Pair d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
-  return d;
-}
-__device__ __forceinline__ Pair vadd(Pair a, Pair b) {
-  Pair d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
-  return d;
-}
-__device__ __forceinline__ Pair make_packet(const float* vals, Pair) {
-  Pair d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d.v) : "f"(vals[0]), "f"(vals[1]));
-  return d;
-}
-__device__ __forceinline__ void split_packet(Pair a, float* vals) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(vals[0]), "=f"(vals[1]) : "l"(a.v));
-}
-__device__ __forceinline__ float hsum(Pair a) {
-  float v[2];
-  split_packet(a, v);
-  return v[0] + v[1];
-}
-__device__ __forceinline__ float vfma(float a, float b, float c) { return fmaf(a, b, c); }
-__device__ __forceinline__ double vfma(double a, double b, double c) { return fma(a, b, c); }
-__device__ __forceinline__ float vmul(float a, float b) { return a * b; }
-__device__ __forceinline__ double vmul(double a, double b) { return a * b; }
-__device__ __forceinline__ float hsum(float a) { return a; }
-__device__ __forceinline__ double hsum(double a) { return a; }
-__device__ __forceinline__ float make_packet(const float* vals, float) { return vals[0]; }
-__device__ __forceinline__ double make_packet(const double* vals, double) { return vals[0]; }
-__device__ __forceinline__ void split_packet(float a, float* vals) { vals[0] = a; }
-__device__ __forceinline__ void split_packet(double a, double* vals) { vals[0] = a; }
-template <typename V>
-__device__ __forceinline__ V zero_packet() {
-  if constexpr (sizeof(V) == sizeof(Pair) && !std::is_floating_point<V>::value) {
-    return V{0ull};
-  } else {
-    return V(0);
-  }
-}
-
-// Memory row [channel][component] (CPL x D, this lane's channels) -> packets [component][packet].
-template <typename T, int CPL, int D>
-__device__ __forceinline__ void load_packets(const T* p, typename Pk<T, CPL>::V* out) {
-  using V = typename Pk<T, CPL>::V;
-  constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
-  T row[CPL * D];
-  load_vectors<T, CPL, D>(p, row);
-#pragma unroll
-  for (int i = 0; i < D; ++i)
-#pragma unroll
-    for (int q = 0; q < NP; ++q) {
-      T vals[W];
-#pragma unroll
-      for (int c = 0; c < W; ++c) vals[c] = row[(q * W + c) * D + i];
-      out[i * NP + q] = make_packet(vals, V{});
-    }
-}
-template <typename T, int CPL, int D>
-__device__ __forceinline__ void unpack_packets(const typename Pk<T, CPL>::V* in, T* row) {
-  constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
-#pragma unroll
-  for (int i = 0; i < D; ++i)
-#pragma unroll
-    for (int q = 0; q < NP; ++q) {
-      T vals[W];
-      split_packet(in[i * NP + q], vals);
-#pragma unroll
-      for (int c = 0; c < W; ++c) row[(q * W + c) * D + i] = vals[c];
-    }
-}
-
-// The lane's CPL consecutive channels of one component (already adjacent in memory) as packets.
+// packet shape of the backward kernel (see uvu_packets.cuh)
 template <typename T, int CPL>
-__device__ __forceinline__ void load_lane_packets(const T* p, typename Pk<T, CPL>::V* out) {
-  if constexpr (Pk<T, CPL>::W == 2) {
-    if constexpr (CPL == 4) {
-      const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(p);
-      out[0].v = t.x;
-      out[1].v = t.y;
-    } else {
-      out[0].v = *reinterpret_cast<const unsigned long long*>(p);
-    }
-  } else {
-    load_vectors<T, CPL, 1>(p, out);
-  }
-}
-
-// One row of a coupling matrix (D3P entries, each stored W times) from shared memory; every lane reads the same
-// address, so each load is one broadcast.  Rows start on 16-byte boundaries except in FP32 without duplication (8).
-template <typename T, int W, int D3P, typename V>
-__device__ __forceinline__ void load_matrix_row(const T* p, V* row) {
-  if constexpr (W == 2) {  // two packets per 128-bit load
-    static_assert(D3P % 2 == 0, "row length must be even");
-    const ulonglong2* v = reinterpret_cast<const ulonglong2*>(p);
-#pragma unroll
-    for (int n = 0; n < D3P / 2; ++n) {
-      const ulonglong2 t = v[n];
-      row[2 * n].v = t.x;
-      row[2 * n + 1].v = t.y;
-    }
-  } else {
-    constexpr int per = (sizeof(T) == 4 ? 8 : 16) / sizeof(T);
-    static_assert(D3P % per == 0, "row length must be a whole number of vectors");
-    const Vec<T, per>* v = reinterpret_cast<const Vec<T, per>*>(p);
-#pragma unroll
-    for (int n = 0; n < D3P / per; ++n) {
-      const Vec<T, per> t = v[n];
-#pragma unroll
-      for (int c = 0; c < per; ++c) row[n * per + c] = t.a[c];
-    }
-  }
-}
+using Pk = PkT<T, CPL, LUNA_BWD_PACKED != 0>;
 
 // Adds the 32 lane contributions of tile rows [0, groups) and writes the entry pairs to gbuf[0 .. 2 * groups).
 // Lanes L and L + 16 share row L: each adds one half of the contributions, a shuffle joins the halves.  Called from
@@ -361,7 +220,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
         constexpr int l1 = decltype(l1c)::value;
         constexpr int d1 = 2 * l1 + 1;
         if (F.x_off[l1] >= 0)
-          load_packets<T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1), &xr[l1 * l1 * NP]);
+          load_packets<Pk<T, CPL>, T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1), &xr[l1 * l1 * NP]);
       });
     }
 #pragma unroll
@@ -385,7 +244,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
         constexpr int d3 = 2 * l3 + 1;
         constexpr int d3p = d3 + 1;
         V g2[d3 * NP];
-        load_packets<T, CPL, d3>(unit + F.ug_soff[l3] + lane * (CPL * d3), g2);
+        load_packets<Pk<T, CPL>, T, CPL, d3>(unit + F.ug_soff[l3] + lane * (CPL * d3), g2);
         static_for<0, LX + 1>([&](auto l1c) {
           constexpr int l1 = decltype(l1c)::value;
           constexpr int d1 = 2 * l1 + 1;
@@ -395,7 +254,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
             const int4 rec = ptab[q];
             const int m_off = rec.y;
             V w2[NP];  // a lane's consecutive channels are already adjacent in memory
-            load_lane_packets<T, CPL>(unit + rec.x + lane * CPL, w2);
+            load_lane_packets<Pk<T, CPL>, T, CPL>(unit + rec.x + lane * CPL, w2);
             const V* xl = &xr[l1 * l1 * NP];
             V* gxl = &gxr[l1 * l1 * NP];
             // rows go to the tile in chunks that fit it; a chunk that does not fit behind what the tile holds
@@ -452,7 +311,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
             }
             if (want_w) {
               T gwv[CPL];
-              unpack_packets<T, CPL, 1>(dot, gwv);
+              unpack_packets<Pk<T, CPL>, T, CPL, 1>(dot, gwv);
               T* dstw = P.gw + static_cast<int64_t>(e0) * F.W + rec.z + lane * CPL;
               if (P.acc_w) {
                 T old[CPL];
@@ -545,7 +404,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
         if (F.x_off[l1] >= 0) {
           T* dstx = P.gx + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1);
           T row[CPL * d1];  // memory order: channel-major, component-minor
-          unpack_packets<T, CPL, d1>(&gxr[l1 * l1 * NP], row);
+          unpack_packets<Pk<T, CPL>, T, CPL, d1>(&gxr[l1 * l1 * NP], row);
           if (P.acc_x) {
             T old[CPL * d1];
             load_vectors<T, CPL, d1>(dstx, old);

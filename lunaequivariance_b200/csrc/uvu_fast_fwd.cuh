@@ -8,14 +8,22 @@
 //
 // FP32 arithmetic runs on packed two-wide FMAs (fma.rn.f32x2): on B200 the scalar FFMA rate is about 0.7 of the
 // packed rate, and packing halves the instruction count of the loop, which is what limits this kernel (issue slots
-// and instruction-cache footprint), not bytes.  Two consecutive channels of a lane form a pair; the per-edge
-// coupling matrices are stored duplicated (m, m) in shared memory so that they arrive as ready-made pairs.
+// and instruction-cache footprint), not bytes.  Two consecutive channels of a lane form a pair that lives in one
+// 64-bit register from the moment it is formed: x pairs are formed once per edge from scalar shared-memory loads,
+// weights arrive as ready-made pairs, accumulators are unpacked only when a node is flushed.  The per-edge coupling
+// matrices are stored once; a matrix entry enters the packed FMA as a broadcast operand.  Every path is evaluated
+// as out_k += sum_i M[i][k] * (x_i * w): the accumulators are the only long-lived operands of the FMAs.
+//
+// What limits the kernel is the latency of a path's shared-memory loads in front of its arithmetic, with only two
+// warps per scheduler to hide it.  For the canonical full path lists (see canon_ok) the loops over paths are
+// therefore unrolled from compile-time tables, so that the loads of the next path are issued during the
+// arithmetic of the current one; a lane also keeps its share of the coupling-matrix program in registers.
 #pragma once
 
 #include <algorithm>
 #include <cstdlib>
 
-#include "uvu_fast.cuh"
+#include "uvu_packets.cuh"
 
 namespace luna {
 namespace fastk {
@@ -37,30 +45,46 @@ struct FwdParams {
   int accumulate;
 };
 
+// packet shape of the forward kernel: FP32 pairs whenever a lane has an even number of channels
+template <typename T, int CPL>
+using FPk = PkT<T, CPL, UsePairs<T, CPL>::value>;
+
 template <typename T, int CPL>
 __host__ __device__ inline size_t fwd_fixed_bytes(const FastMeta& f) {
-  // M buffer (duplicated entries on the packed path), y row, barriers
-  const size_t m_elems = static_cast<size_t>(f.m_total) * (UsePairs<T, CPL>::value ? 2 : 1);
+  // M buffer (padded to whole rounds of 32 entries), y row, barriers
+  const size_t m_elems = static_cast<size_t>(f.m_total + 31) / 32 * 32;
   return (m_elems + 32) * sizeof(T) + kMaxStages * sizeof(uint64_t);
 }
 
-template <typename T, int CPL, int LX, int LO>
+// Register budget of the coupling-matrix program: a lane keeps the two terms of up to this many entries in
+// registers (3 registers each); longer programs are read from shared memory.
+constexpr int kMaxProgramRounds = 12;
+
+// L2 >= 0: the path list is the canonical full list for (LX, L2, LO) and the loops over paths are unrolled from
+// compile-time tables.  L2 < 0: any path list, loops over paths read the tables in FastMeta.
+template <typename T, int CPL, int LX, int LO, int L2>
 __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __grid_constant__ FwdParams<T> P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  constexpr bool kPairs = UsePairs<T, CPL>::value;
-  constexpr int NP = CPL / 2;  // channel pairs per lane (packed path)
+  using PK = FPk<T, CPL>;
+  using V = typename PK::V;
+  constexpr int NP = PK::NP;
+  constexpr bool kCanon = L2 >= 0;
+  constexpr int kCanonTotal = kCanon ? canon_moff(LX, L2 < 0 ? 0 : L2, LO, -1, -1, -1) : 0;
+  constexpr int kRounds = (kCanonTotal + 31) / 32;
+  constexpr bool kProgramInRegisters = kCanon && kRounds <= kMaxProgramRounds;
   const FastMeta& F = P.meta;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int stages = P.stages;
   const int stage_elems = F.w_stage_elems + F.x_stage_elems;
+  const int m_total = kCanon ? kCanonTotal : F.m_total;
   const T* ell_c;
   const unsigned char* ell_j;
-  load_ell<T>(smem_raw, P.ell_c, P.ell_j, F.m_total, F.m_terms, &ell_c, &ell_j);
+  load_ell<T>(smem_raw, P.ell_c, P.ell_j, m_total, F.m_terms, &ell_c, &ell_j);
   const size_t warp_bytes = static_cast<size_t>(stages) * stage_elems * sizeof(T) + fwd_fixed_bytes<T, CPL>(F);
-  unsigned char* base = smem_raw + ell_bytes<T>(F.m_total, F.m_terms) + static_cast<size_t>(warp) * warp_bytes;
+  unsigned char* base = smem_raw + ell_bytes<T>(m_total, F.m_terms) + static_cast<size_t>(warp) * warp_bytes;
   T* stage_mem = reinterpret_cast<T*>(base);
   T* mbuf = stage_mem + static_cast<size_t>(stages) * stage_elems;
-  T* ybuf = mbuf + F.m_total * (kPairs ? 2 : 1);
+  T* ybuf = mbuf + (m_total + 31) / 32 * 32;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ybuf + 32);
 
   if (lane == 0) {
@@ -68,6 +92,20 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
     fence_barrier_init();
   }
   __syncwarp();
+
+  // the lane's share of the coupling-matrix program: entries lane, lane + 32, ...
+  T prog_a[kProgramInRegisters ? kRounds : 1], prog_b[kProgramInRegisters ? kRounds : 1];
+  unsigned prog_j[kProgramInRegisters ? kRounds : 1];
+  if constexpr (kProgramInRegisters) {
+#pragma unroll
+    for (int r = 0; r < kRounds; ++r) {
+      const int m = r * 32 + lane;
+      const bool in = m < m_total;
+      prog_a[r] = in ? ell_c[m] : T(0);
+      prog_b[r] = in ? ell_c[m_total + m] : T(0);
+      prog_j[r] = in ? (static_cast<unsigned>(ell_j[m]) | (static_cast<unsigned>(ell_j[m_total + m]) << 8)) : 0u;
+    }
+  }
 
   const int chw = 32 * CPL;
   const int c0 = blockIdx.y * chw;  // first channel of this warp's chunk
@@ -110,17 +148,37 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
   int src_ahead = e_begin + stages < e_end ? P.src[e_begin + stages] : 0;
 
   T y_next = (lane < F.Y && e_begin < e_end) ? P.y[e_begin * F.Y + lane] : T(0);
-  constexpr int AR = (LO + 1) * (LO + 1) * CPL;
-  T acc[AR];  // packed path: viewed as pairs, element (l3, k, pair) at l3*l3*CPL + (k*NP + pair)*2
+  constexpr int AR = (LO + 1) * (LO + 1) * NP;
+  constexpr int XR = (LX + 1) * (LX + 1) * NP;
+  V acc[AR];  // packet (l3, k, p) at l3 * l3 * NP + k * NP + p
   int64_t e = e_begin;
   int s = 0;
   uint32_t parity = 0;
   bool alive = true;
 
+  // out_k += sum_i M[i][k] * (x_i * w) for one path; the matrix is stored once and broadcast into both halves
+  auto path_body = [&](auto l1c, auto l3c, const T* wq, const T* matrix, const V* xl, V* al) {
+    constexpr int l1 = decltype(l1c)::value, l3 = decltype(l3c)::value;
+    constexpr int d1 = 2 * l1 + 1, d3 = 2 * l3 + 1, d3p = d3 + 1;
+    V w2[NP];  // a lane's consecutive channels are already adjacent in memory
+    load_lane_packets<PK, T, CPL>(wq, w2);
+    static_for<0, d1>([&](auto ic) {
+      constexpr int i = decltype(ic)::value;
+      T mrow[d3p];
+      load_plain_row<T, d3p, i>(matrix, mrow);
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        const V xw = vmul(xl[i * NP + p], w2[p]);
+#pragma unroll
+        for (int k = 0; k < d3; ++k) al[k * NP + p] = vfma(bcast_packet(mrow[k], V{}), xw, al[k * NP + p]);
+      }
+    });
+  };
+
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t ee = P.dst_rowptr[n + 1];
 #pragma unroll
-    for (int a = 0; a < AR; ++a) acc[a] = T(0);
+    for (int a = 0; a < AR; ++a) acc[a] = zero_packet<V>();
 #pragma unroll 1
     for (; e < ee; ++e) {
       if (!mbar_wait_bounded(&bars[s], parity)) {
@@ -133,57 +191,45 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
       // coupling matrices of this edge
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
-      compute_m_share<T, kPairs>(ell_c, ell_j, ybuf, mbuf, F.m_total, 0, 1, lane);
+      if constexpr (kProgramInRegisters) {
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r)
+          mbuf[r * 32 + lane] = fma(prog_b[r], ybuf[prog_j[r] >> 8], prog_a[r] * ybuf[prog_j[r] & 255u]);
+      } else {
+        compute_m_share<T, false>(ell_c, ell_j, ybuf, mbuf, m_total, 0, 1, lane);
+      }
       if (e + 1 < e_end && lane < F.Y) y_next = P.y[(e + 1) * F.Y + lane];
-      __syncwarp();
-
+      // this lane's x packets, formed once per edge: packet (l1, i, p) at l1 * l1 * NP + i * NP + p
+      V xr[XR];
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         constexpr int d1 = 2 * l1 + 1;
-        if (F.x_off[l1] < 0) return;
-        T xl[CPL * d1];
-        load_vectors<T, CPL, d1>(xs + F.xs_off[l1] + lane * (CPL * d1), xl);
+        if (kCanon || F.x_off[l1] >= 0)
+          load_packets_scalar<PK, T, CPL, d1>(xs + (kCanon ? chw * l1 * l1 : F.xs_off[l1]) + lane * (CPL * d1),
+                                              &xr[l1 * l1 * NP]);
+      });
+      __syncwarp();
+
+      const T* wl = ws + lane * CPL;
+      static_for<0, LX + 1>([&](auto l1c) {
+        constexpr int l1 = decltype(l1c)::value;
+        if (!kCanon && F.x_off[l1] < 0) return;
+        const V* xl = &xr[l1 * l1 * NP];
         static_for<0, LO + 1>([&](auto l3c) {
           constexpr int l3 = decltype(l3c)::value;
-          constexpr int d3 = 2 * l3 + 1;
-          constexpr int d3p = d3 + 1;  // row stride of the coupling matrices
-          const int q_end = F.pair_ptr[l3 * (kMaxFastL + 1) + l1 + 1];
+          V* al = &acc[l3 * l3 * NP];
+          if constexpr (kCanon) {
+            static_for<0, (L2 < 0 ? 0 : L2) + 1>([&](auto l2c) {
+              constexpr int l2 = decltype(l2c)::value;
+              if constexpr (canon_ok(LX, L2, LO, l1, l2, l3))
+                path_body(l1c, l3c, wl + canon_wrank(LX, L2, LO, l1, l2, l3) * chw,
+                          mbuf + canon_moff(LX, L2, LO, l1, l2, l3), xl, al);
+            });
+          } else {
+            const int q_end = F.pair_ptr[l3 * (kMaxFastL + 1) + l1 + 1];
 #pragma unroll 1
-          for (int q = F.pair_ptr[l3 * (kMaxFastL + 1) + l1]; q < q_end; ++q) {
-            T wv[CPL];
-            load_vectors<T, CPL, 1>(ws + F.w_soff[q] + lane * CPL, wv);
-            T* al = &acc[l3 * l3 * CPL];
-            if constexpr (kPairs) {
-              // matrix entries arrive duplicated: mr2[m] = (M[m], M[m])
-              float2 mr2[d1 * d3p];
-              load_matrix<T, 2 * d1 * d3p>(mbuf + 2 * F.m_off[q], reinterpret_cast<T*>(mr2));
-#pragma unroll
-              for (int p = 0; p < NP; ++p) {
-                const float2 w2 = make_float2(wv[2 * p], wv[2 * p + 1]);
-#pragma unroll
-                for (int k = 0; k < d3; ++k) {
-                  float2 t = mul2(mr2[k], make_float2(xl[(2 * p) * d1], xl[(2 * p + 1) * d1]));
-#pragma unroll
-                  for (int i = 1; i < d1; ++i)
-                    t = fma2(mr2[i * d3p + k], make_float2(xl[(2 * p) * d1 + i], xl[(2 * p + 1) * d1 + i]), t);
-                  float2* a2 = reinterpret_cast<float2*>(al) + (k * NP + p);
-                  *a2 = fma2(w2, t, *a2);
-                }
-              }
-            } else {
-              T mr[d1 * d3p];
-              load_matrix<T, d1 * d3p>(mbuf + F.m_off[q], mr);
-#pragma unroll
-              for (int c = 0; c < CPL; ++c) {
-#pragma unroll
-                for (int k = 0; k < d3; ++k) {
-                  T t = mr[k] * xl[c * d1];
-#pragma unroll
-                  for (int i = 1; i < d1; ++i) t = fma(mr[i * d3p + k], xl[c * d1 + i], t);
-                  al[c * d3 + k] = fma(wv[c], t, al[c * d3 + k]);
-                }
-              }
-            }
+            for (int q = F.pair_ptr[l3 * (kMaxFastL + 1) + l1]; q < q_end; ++q)
+              path_body(l1c, l3c, wl + F.w_soff[q], mbuf + F.m_off[q], xl, al);
           }
         });
       });
@@ -203,20 +249,8 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
       constexpr int d3 = 2 * l3 + 1;
       if (F.o_off[l3] >= 0) {
         T* dst = P.out + n * F.O + F.o_off[l3] + c0 * d3 + lane * (CPL * d3);
-        T* al = &acc[l3 * l3 * CPL];
         T row[CPL * d3];  // memory order: channel-major, component-minor
-        if constexpr (kPairs) {
-#pragma unroll
-          for (int p = 0; p < NP; ++p)
-#pragma unroll
-            for (int k = 0; k < d3; ++k) {
-              row[(2 * p) * d3 + k] = al[(k * NP + p) * 2];
-              row[(2 * p + 1) * d3 + k] = al[(k * NP + p) * 2 + 1];
-            }
-        } else {
-#pragma unroll
-          for (int a = 0; a < CPL * d3; ++a) row[a] = al[a];
-        }
+        unpack_packets<PK, T, CPL, d3>(&acc[l3 * l3 * NP], row);
         if (P.accumulate) {
           T old[CPL * d3];
           load_vectors<T, CPL, d3>(dst, old);
@@ -240,7 +274,7 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
 }
 
 
-template <typename T, int CPL, int LX, int LO>
+template <typename T, int CPL, int LX, int LO, int L2>
 int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
                         const T* y, const T* w, T* out, bool accumulate, cudaStream_t stream) {
   const FastMeta& f = plan->fast;
@@ -259,7 +293,7 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.num_edges = graph->num_edges;
   P.accumulate = accumulate ? 1 : 0;
   const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
-  auto kernel = fast_fwd_kernel<T, CPL, LX, LO>;
+  auto kernel = fast_fwd_kernel<T, CPL, LX, LO, L2>;
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
   const Residency r = choose_residency(stage, fwd_fixed_bytes<T, CPL>(f), ell_bytes<T>(f.m_total, f.m_terms),
@@ -278,15 +312,24 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   return LUNA_OK;
 }
 
-// Dispatch on the degree class: the smallest compiled (LX, LO) that covers the plan.
+// Dispatch: a kernel unrolled for the canonical full path list if the plan has one of the compiled shapes, else
+// the smallest compiled degree class (LX, LO) that covers the plan, with loops over the plan's path tables.
 template <typename T, int CPL>
 int launch_fast_fwd(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
                     const T* y, const T* w, T* out, bool accumulate, cudaStream_t stream) {
-  const int lx = plan->fast.LX, lo = plan->fast.LO;
-  if (lx <= 1 && lo <= 1) return launch_fast_fwd_one<T, CPL, 1, 1>(plan, dt, graph, x, y, w, out, accumulate, stream);
-  if (lx <= 2 && lo <= 2) return launch_fast_fwd_one<T, CPL, 2, 2>(plan, dt, graph, x, y, w, out, accumulate, stream);
-  if (lx <= 2 && lo <= 3) return launch_fast_fwd_one<T, CPL, 2, 3>(plan, dt, graph, x, y, w, out, accumulate, stream);
-  return launch_fast_fwd_one<T, CPL, 3, 3>(plan, dt, graph, x, y, w, out, accumulate, stream);
+  const int lx = plan->fast.LX, lo = plan->fast.LO, l2 = plan->fast.canon_l2;
+#define LUNA_FWD_ARGS plan, dt, graph, x, y, w, out, accumulate, stream
+  if (std::getenv("LUNA_B200_NO_CANON") == nullptr) {
+    if (lx == 2 && l2 == 3 && lo == 3) return launch_fast_fwd_one<T, CPL, 2, 3, 3>(LUNA_FWD_ARGS);
+    if (lx == 2 && l2 == 2 && lo == 2) return launch_fast_fwd_one<T, CPL, 2, 2, 2>(LUNA_FWD_ARGS);
+    if (lx == 3 && l2 == 3 && lo == 3) return launch_fast_fwd_one<T, CPL, 3, 3, 3>(LUNA_FWD_ARGS);
+    if (lx == 1 && l2 == 1 && lo == 1) return launch_fast_fwd_one<T, CPL, 1, 1, 1>(LUNA_FWD_ARGS);
+  }
+  if (lx <= 1 && lo <= 1) return launch_fast_fwd_one<T, CPL, 1, 1, -1>(LUNA_FWD_ARGS);
+  if (lx <= 2 && lo <= 2) return launch_fast_fwd_one<T, CPL, 2, 2, -1>(LUNA_FWD_ARGS);
+  if (lx <= 2 && lo <= 3) return launch_fast_fwd_one<T, CPL, 2, 3, -1>(LUNA_FWD_ARGS);
+  return launch_fast_fwd_one<T, CPL, 3, 3, -1>(LUNA_FWD_ARGS);
+#undef LUNA_FWD_ARGS
 }
 
 }  // namespace fastk
