@@ -192,9 +192,49 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl) {
       const int l1 = (p.d1 - 1) / 2, l2 = (p.d2 - 1) / 2, l3 = (p.d3 - 1) / 2;
       canon = (p.d1 % 2 == 1) && (p.d2 % 2 == 1) && (p.d3 % 2 == 1) && fastk::canon_ok(f.LX, L2, f.LO, l1, l2, l3) &&
               f.w_soff[q] == fastk::canon_wrank(f.LX, L2, f.LO, l1, l2, l3) * chw &&
+              p.w_off == fastk::canon_wrank(f.LX, L2, f.LO, l1, l2, l3) * ch &&
               f.m_off[q] == fastk::canon_moff(f.LX, L2, f.LO, l1, l2, l3);
     }
     if (canon) f.canon_l2 = L2;
+    // sparse term list: every path's terms must have exactly the compiled-in pattern
+    f.sparse_terms = 0;
+    plan->sp_c.clear();
+    plan->sp_j.clear();
+    if (canon && L2 <= 3 && f.LX <= 3 && f.LO <= 3) {
+      const int total_terms = fastk::canon_toff(f.LX, L2, f.LO, -1, -1, -1);
+      std::vector<double> sc(static_cast<size_t>(total_terms), 0.0);
+      std::vector<unsigned char> sj(static_cast<size_t>(total_terms), 0);
+      bool match = true;
+      for (size_t q = 0; q < order.size() && match; ++q) {
+        const PathRec& p = paths[order[q]];
+        const int l1 = (p.d1 - 1) / 2, l2 = (p.d2 - 1) / 2, l3 = (p.d3 - 1) / 2;
+        const fastk::CgTerm* pattern = fastk::cg_pattern(l1, l2, l3);
+        const int n = fastk::cg_count(l1, l2, l3);
+        const int toff = fastk::canon_toff(f.LX, L2, f.LO, l1, l2, l3);
+        match = pattern != nullptr && p.y_off == l2 * l2;
+        int found = 0;
+        for (int k = 0; k < p.d3 && match; ++k)
+          for (int t = plan->rowptr_k[p.byk_ptr + k]; t < plan->rowptr_k[p.byk_ptr + k + 1] && match; ++t) {
+            const auto& term = plan->terms_k[t];  // (a, b) = (i, j)
+            int slot = -1;
+            for (int u = 0; u < n; ++u)
+              if (pattern[u].i == term.a && pattern[u].j == term.b && pattern[u].k == k) slot = u;
+            if (slot < 0 || sc[toff + slot] != 0.0) {
+              match = false;
+            } else {
+              sc[toff + slot] = term.c;
+              sj[toff + slot] = static_cast<unsigned char>(p.y_off + term.b);
+              ++found;
+            }
+          }
+        if (found != n) match = false;  // a pattern entry the plan does not have would be a wasted (zero) term
+      }
+      if (match) {
+        f.sparse_terms = total_terms;
+        plan->sp_c = sc;
+        plan->sp_j = sj;
+      }
+    }
   }
 
   // the program in padded (ELL) form for the kernels: term t of entry m at [t * m_total + m], exactly two
@@ -364,6 +404,17 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
     std::memcpy(blob.data() + f.tb_ellj, plan->ell_j.data(), plan->ell_j.size());
   }
   const size_t o_blob = append(blob.data(), blob.size());
+  std::vector<unsigned char> spc(plan->sp_c.size() * scalar);
+  for (size_t i = 0; i < plan->sp_c.size(); ++i) {
+    if (f64) {
+      std::memcpy(spc.data() + i * 8, &plan->sp_c[i], 8);
+    } else {
+      float v = static_cast<float>(plan->sp_c[i]);
+      std::memcpy(spc.data() + i * 4, &v, 4);
+    }
+  }
+  const size_t o_spc = append(spc.data(), spc.size());
+  const size_t o_spj = append(plan->sp_j.data(), plan->sp_j.size());
 
   DeviceTables dt;
   dt.bytes = host.size();
@@ -392,6 +443,8 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   dt.ell_j = base + o_mj;
   dt.ell_c = base + o_mc;
   dt.bwd_tables = base + o_blob;
+  dt.sp_c = base + o_spc;
+  dt.sp_j = base + o_spj;
   LUNA_CUDA_CHECK(cudaDeviceGetAttribute(&dt.sm_count, cudaDevAttrMultiProcessorCount, device));
   LUNA_CUDA_CHECK(cudaDeviceGetAttribute(&dt.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   auto inserted = plan->device_tables.emplace(device, dt);

@@ -65,6 +65,8 @@ struct CopyPiece {
 struct FastMeta {
   int LX, LO;                 // highest degree present in x / out
   int canon_l2;               // highest edge-harmonic degree if the path list is the canonical full list, else -1
+  int sparse_terms;           // length of the sparse term list (canon_toff total) if the plan's coupling terms have
+                              // the compiled-in patterns and y is laid out as degrees 0..L2 in order, else 0
   int cpl;                    // channels per lane
   int chunks;                 // channel chunks per feature block (a warp handles 32 * cpl channels)
   int ch;                     // channels per block (uniform)
@@ -116,6 +118,9 @@ struct DeviceTables {
   // entry indices of the edge-attribute gradient's program (gy[j] = sum_t c[t] * G[m[t]]), y indices of the
   // padded program; offsets in FastMeta::tb_*
   const unsigned char* bwd_tables = nullptr;
+  // sparse term list of a canonical plan (FastMeta::sparse_terms entries): coefficient and y index of each term
+  const void* sp_c = nullptr;
+  const unsigned char* sp_j = nullptr;
   int sm_count = 0;
   int max_smem_optin = 0;
 };
@@ -145,6 +150,8 @@ struct luna_uvu_plan {
   std::vector<unsigned char> ell_j;
   std::vector<int> gy_ptr, gy_m;
   std::vector<double> gy_c;
+  std::vector<double> sp_c;
+  std::vector<unsigned char> sp_j;
 
   std::mutex mutex;
   std::map<int, luna::DeviceTables> device_tables;

@@ -46,14 +46,17 @@ Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_
 }
 
 int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count) {
-  // A small graph still fills one wave: fewer edges per warp (not below 48) rather than idle SMs.
-  const int64_t wave = static_cast<int64_t>(sm_count) * r.ctas;
-  const int64_t fill = num_edges / std::max<int64_t>(1, wave * r.warps);
-  const int64_t per_warp = std::max<int64_t>(48, std::min<int64_t>(edges_per_warp(target), fill));
-  const int64_t warps = std::max<int64_t>(1, ceil_div(num_edges, per_warp));
-  int64_t blocks = ceil_div(warps, r.warps);
-  if (blocks > wave) blocks = ceil_div(blocks, wave) * wave;
-  return blocks;
+  const int64_t wave = static_cast<int64_t>(sm_count) * r.ctas;  // CTAs resident at once
+  const int64_t wave_warps = wave * r.warps;
+  const int64_t per_warp = edges_per_warp(target);
+  if (num_edges > per_warp * wave_warps) {  // several waves of about `target` edges per warp, whole waves only
+    const int64_t blocks = ceil_div(ceil_div(num_edges, per_warp), r.warps);
+    return ceil_div(blocks, wave) * wave;
+  }
+  // a small graph gets exactly one wave (fewer edges per warp rather than idle SMs), or less if even 48 edges per
+  // warp do not fill one
+  if (num_edges >= 48 * wave_warps) return wave;
+  return std::max<int64_t>(1, ceil_div(ceil_div(num_edges, 48), r.warps));
 }
 
 // Explicit instantiations live in uvu_fast_fwd_*.cu so that they compile in parallel.

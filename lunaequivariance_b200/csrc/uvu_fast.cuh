@@ -19,6 +19,7 @@
 #include <cstdlib>
 #include <type_traits>
 
+#include "cg_patterns.h"
 #include "plan.h"
 
 namespace luna {
@@ -227,6 +228,32 @@ __host__ __device__ constexpr int canon_moff(int LX, int L2, int LO, int a, int 
         while (m % 4) ++m;
       }
   return m;
+}
+
+// number of canonical paths into degree c that come before (a, b) in (l1, l2) order; past-the-end arguments give
+// the number of paths into that degree
+__host__ __device__ constexpr int canon_unit_index(int LX, int L2, int LO, int a, int b, int c) {
+  int r = 0;
+  for (int l1 = 0; l1 <= LX; ++l1)
+    for (int l2 = 0; l2 <= L2; ++l2) {
+      if (l1 == a && l2 == b) return r;
+      if (canon_ok(LX, L2, LO, l1, l2, c)) ++r;
+    }
+  return r;
+}
+
+// first coupling term of the path in the sparse term list: paths in (l3, l1, l2) order, every path's terms (in the
+// (i, k, j) order of CgPattern) padded to a multiple of four; past-the-end arguments give the total
+__host__ __device__ constexpr int canon_toff(int LX, int L2, int LO, int a, int b, int c) {
+  int t = 0;
+  for (int l3 = 0; l3 <= LO; ++l3)
+    for (int l1 = 0; l1 <= LX; ++l1)
+      for (int l2 = 0; l2 <= L2; ++l2) {
+        if (!canon_ok(LX, L2, LO, l1, l2, l3)) continue;
+        if (l1 == a && l2 == b && l3 == c) return t;
+        t += (cg_count(l1, l2, l3) + 3) / 4 * 4;
+      }
+  return t;
 }
 
 // ---- per-edge coupling matrices -------------------------------------------------------------------------------------

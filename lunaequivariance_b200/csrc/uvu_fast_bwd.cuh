@@ -18,6 +18,7 @@
 #pragma once
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "uvu_packets.cuh"
 
@@ -49,18 +50,17 @@ struct BwdParams {
   const int* src_rowptr;
   const int* edge_ids;
   const unsigned char* tables;  // blob described by FastMeta::tb_*
+  const T* sp_c;                // sparse term list of a canonical plan (coefficients, y indices), else null
+  const unsigned char* sp_j;
   int* status;
   int64_t num_src_nodes, num_edges;
   int slots;
   int acc_x, acc_y, acc_w;
 };
 
-#ifndef LUNA_BWD_PACKED
-#define LUNA_BWD_PACKED 0
-#endif
-// packet shape of the backward kernel (see uvu_packets.cuh)
+// packet shape of the backward kernel: FP32 pairs whenever a lane has an even number of channels
 template <typename T, int CPL>
-using Pk = PkT<T, CPL, LUNA_BWD_PACKED != 0>;
+using Pk = PkT<T, CPL, UsePairs<T, CPL>::value>;
 
 // Adds the 32 lane contributions of tile rows [0, groups) and writes the entry pairs to gbuf[0 .. 2 * groups).
 // Lanes L and L + 16 share row L: each adds one half of the contributions, a shuffle joins the halves.  Called from
@@ -109,8 +109,8 @@ __device__ __noinline__ void flush_tile(const T* red, T* gbuf, int groups, int l
 
 template <typename T, int CPL>
 __host__ __device__ inline size_t bwd_fixed_bytes(const FastMeta& f) {
-  // coupling matrices (W copies per entry), G buffer, reduction tile, y row, barriers
-  const size_t elems = static_cast<size_t>(f.m_total) * (Pk<T, CPL>::W + 1) +
+  // coupling matrices (padded to whole rounds of 32 entries), G buffer, reduction tile, y row, barriers
+  const size_t elems = static_cast<size_t>(f.m_total + 31) / 32 * 32 + f.m_total +
                        static_cast<size_t>(kRedGroups) * red_stride<T>() + 32;
   return elems * sizeof(T) + kMaxSlots * sizeof(uint64_t);
 }
@@ -121,17 +121,26 @@ __host__ __device__ inline size_t bwd_shared_bytes(const FastMeta& f) {
 
 // WXW: whether gx and/or gw are produced; WY: whether gy is.  Compiled in or out: each is about half of the kernel,
 // and only the first needs the coupling matrices.
+// L2 >= 0: canonical full path list for (LX, L2, LO), loops over units and paths unrolled from compile-time tables;
+// L2 < 0: any path list, loops read the tables in FastMeta.
 // MAXW warps per CTA at most and MINB CTAs per SM at least: together they cap the registers per thread.
-template <typename T, int CPL, int LX, int LO, bool WXW, bool WY, int MAXW, int MINB>
+template <typename T, int CPL, int LX, int LO, int L2, bool WXW, bool WY, int MAXW, int MINB>
 __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_constant__ BwdParams<T> P) {
-  using V = typename Pk<T, CPL>::V;
-  constexpr int W = Pk<T, CPL>::W, NP = Pk<T, CPL>::NP;
+  using PK = Pk<T, CPL>;
+  using V = typename PK::V;
+  constexpr int NP = PK::NP;
   constexpr int L1S = kMaxFastL + 1;
+  constexpr bool kCanon = L2 >= 0;
+  constexpr int L2c = L2 < 0 ? 0 : L2;
+  constexpr int kCanonTotal = kCanon ? canon_moff(LX, L2c, LO, -1, -1, -1) : 0;
+  constexpr int kRounds = (kCanonTotal + 31) / 32;
+  constexpr bool kProgramInRegisters = kCanon && WXW && kRounds <= 12;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const FastMeta& F = P.meta;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int R = P.slots, nk = F.nkinds;
+  const int R = P.slots, nk = kCanon ? LO + 1 : F.nkinds;
   const int slot_elems = F.slot_elems;
+  const int m_total = kCanon ? kCanonTotal : F.m_total;
   constexpr int chw = 32 * CPL;
   const int c0 = blockIdx.y * chw;
 
@@ -152,8 +161,8 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
   const size_t warp_bytes = static_cast<size_t>(R) * slot_elems * sizeof(T) + bwd_fixed_bytes<T, CPL>(F);
   T* slots = reinterpret_cast<T*>(smem_raw + bwd_shared_bytes(F) + static_cast<size_t>(warp) * warp_bytes);
   T* mbuf = slots + static_cast<size_t>(R) * slot_elems;
-  T* gbuf = mbuf + W * F.m_total;
-  T* red = gbuf + F.m_total;
+  T* gbuf = mbuf + (m_total + 31) / 32 * 32;
+  T* red = gbuf + m_total;
   T* ybuf = red + kRedGroups * red_stride<T>();
   uint64_t* bars = reinterpret_cast<uint64_t*>(ybuf + 32);
 
@@ -162,6 +171,20 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
     fence_barrier_init();
   }
   __syncwarp();
+
+  // the lane's share of the coupling-matrix program: entries lane, lane + 32, ...
+  T prog_a[kProgramInRegisters ? kRounds : 1], prog_b[kProgramInRegisters ? kRounds : 1];
+  unsigned prog_j[kProgramInRegisters ? kRounds : 1];
+  if constexpr (kProgramInRegisters) {
+#pragma unroll
+    for (int r = 0; r < kRounds; ++r) {
+      const int m = r * 32 + lane;
+      const bool in = m < m_total;
+      prog_a[r] = in ? ell_c[m] : T(0);
+      prog_b[r] = in ? ell_c[m_total + m] : T(0);
+      prog_j[r] = in ? (static_cast<unsigned>(ell_j[m]) | (static_cast<unsigned>(ell_j[m_total + m]) << 8)) : 0u;
+    }
+  }
 
   const int64_t E = P.num_edges, N = P.num_src_nodes;
   const int nwarps = blockDim.x >> 5;
@@ -212,6 +235,144 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
   int s = 0;
   uint32_t parity = 0;
   bool alive = true;
+  int tile_base = 0;  // first matrix entry held in the reduction tile
+  int tile_end = 0;   // one past the last entry written to the tile
+
+  // One path of a unit.  wq: the lane's weights in the slot; matrix: the path's coupling matrix (stored once);
+  // m_off: its first entry (index into the G buffer); w_goff: global offset of the lane's weights (for gw).
+  auto path_body = [&](auto l1c, auto l3c, const V* g2, const T* wq, int m_off, int64_t w_goff) {
+    constexpr int l1 = decltype(l1c)::value, l3 = decltype(l3c)::value;
+    constexpr int d1 = 2 * l1 + 1, d3 = 2 * l3 + 1, d3p = d3 + 1;
+    V w2[NP];  // a lane's consecutive channels are already adjacent in memory
+    load_lane_packets<PK, T, CPL>(wq, w2);
+    const V* xl = &xr[l1 * l1 * NP];
+    V* gxl = &gxr[l1 * l1 * NP];
+    // rows go to the tile in chunks that fit it; a chunk that does not fit behind what the tile holds first
+    // reduces that
+    constexpr int rows_per_chunk = (2 * kRedGroups) / d3p < d1 ? (2 * kRedGroups) / d3p : d1;
+    T* tile = nullptr;
+    V dot[NP];
+#pragma unroll
+    for (int p = 0; p < NP; ++p) dot[p] = zero_packet<V>();
+    const T* matrix = mbuf + m_off;
+    static_for<0, d1>([&](auto ic) {
+      constexpr int i = decltype(ic)::value;
+      if (want_y && i % rows_per_chunk == 0) {
+        constexpr int chunk_rows = d1 - i < rows_per_chunk ? d1 - i : rows_per_chunk;
+        const int first = m_off + i * d3p;
+        if (first + chunk_rows * d3p - tile_base > 2 * kRedGroups) {
+          flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
+          tile_base = first;
+        }
+        tile = red + ((first - tile_base) / 2) * red_stride<T>() + lane * 2;
+        tile_end = first + chunk_rows * d3p;
+      }
+      if constexpr (WXW) {
+        T mrow[d3p];
+        load_plain_row<T, d3p, i>(matrix, mrow);
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+          V sv = vmul(bcast_packet(mrow[0], V{}), g2[p]);
+#pragma unroll
+          for (int k = 1; k < d3; ++k) sv = vfma(bcast_packet(mrow[k], V{}), g2[k * NP + p], sv);
+          gxl[i * NP + p] = vfma(w2[p], sv, gxl[i * NP + p]);
+          dot[p] = vfma(xl[i * NP + p], sv, dot[p]);
+        }
+      }
+      if (want_y) {
+        V xw[NP];
+#pragma unroll
+        for (int p = 0; p < NP; ++p) xw[p] = vmul(xl[i * NP + p], w2[p]);
+        T grow[d3p];
+#pragma unroll
+        for (int k = 0; k < d3; ++k) {
+          V acc = vmul(xw[0], g2[k * NP]);
+#pragma unroll
+          for (int p = 1; p < NP; ++p) acc = vfma(xw[p], g2[k * NP + p], acc);
+          grow[k] = hsum(acc);
+        }
+        grow[d3] = T(0);
+#pragma unroll
+        for (int kk = 0; kk < d3p / 2; ++kk) {
+          Vec<T, 2> pr{{grow[2 * kk], grow[2 * kk + 1]}};
+          *reinterpret_cast<Vec<T, 2>*>(tile + ((i % rows_per_chunk) * (d3p / 2) + kk) * red_stride<T>()) = pr;
+        }
+      }
+    });
+    if (want_w) {
+      T gwv[CPL];
+      unpack_packets<PK, T, CPL, 1>(dot, gwv);
+      T* dstw = P.gw + w_goff;
+      if (P.acc_w) {
+        T old[CPL];
+        load_vectors<T, CPL, 1>(dstw, old);
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) gwv[c] += old[c];
+      }
+      store_vectors_streaming<T, CPL, 1>(dstw, gwv);
+    }
+  };
+
+  // One unit = the paths into output degree l3 of the current edge.
+  auto unit_body = [&](auto l3c, const T* unit) {
+    constexpr int l3 = decltype(l3c)::value;
+    constexpr int d3 = 2 * l3 + 1;
+    V g2[d3 * NP];
+    const int64_t w_row = static_cast<int64_t>(e0) * F.W + lane * CPL;
+    if constexpr (kCanon) {
+      constexpr int paths_here = canon_unit_index(LX, L2c, LO, -1, -1, l3);
+      load_packets_scalar<PK, T, CPL, d3>(unit + paths_here * chw + lane * (CPL * d3), g2);
+      static_for<0, LX + 1>([&](auto l1c) {
+        constexpr int l1 = decltype(l1c)::value;
+        static_for<0, L2c + 1>([&](auto l2c) {
+          constexpr int l2 = decltype(l2c)::value;
+          if constexpr (canon_ok(LX, L2c, LO, l1, l2, l3))
+            path_body(l1c, l3c, g2, unit + canon_unit_index(LX, L2c, LO, l1, l2, l3) * chw + lane * CPL,
+                      canon_moff(LX, L2c, LO, l1, l2, l3),
+                      w_row + canon_wrank(LX, L2c, LO, l1, l2, l3) * F.ch + c0);
+        });
+      });
+    } else {
+      load_packets_scalar<PK, T, CPL, d3>(unit + F.ug_soff[l3] + lane * (CPL * d3), g2);
+      static_for<0, LX + 1>([&](auto l1c) {
+        constexpr int l1 = decltype(l1c)::value;
+        const int q_end = F.pair_ptr[l3 * L1S + l1 + 1];
+#pragma unroll 1
+        for (int q = F.pair_ptr[l3 * L1S + l1]; q < q_end; ++q) {
+          const int4 rec = ptab[q];
+          path_body(l1c, l3c, g2, unit + rec.x + lane * CPL, rec.y, w_row + rec.z);
+        }
+      });
+    }
+  };
+
+  // waits for the unit in slot s, runs it and refills the slot with the unit R places later
+  auto run_unit = [&](auto l3c, int kind) -> bool {
+    if (!mbar_wait_bounded(&bars[s], parity)) {
+      if (lane == 0) atomicExch(P.status, 2);
+      return false;
+    }
+    unit_body(l3c, slots + static_cast<size_t>(s) * slot_elems);
+    __syncwarp();  // every lane is done with this slot
+    if (u + R < total_units) {
+      int next = kind + R, de = 0;
+      if (next >= nk) {
+        next -= nk;
+        de = 1;
+      }
+      if (next >= nk) {
+        next -= nk;
+        de = 2;
+      }
+      issue(next, de == 0 ? e0 : (de == 1 ? e1 : e2), de == 0 ? d0 : (de == 1 ? d1n : d2n), s);
+    }
+    ++u;
+    if (++s == R) {
+      s = 0;
+      parity ^= 1u;
+    }
+    return true;
+  };
 
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t pe = P.src_rowptr[n + 1];
@@ -219,8 +380,9 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         constexpr int d1 = 2 * l1 + 1;
-        if (F.x_off[l1] >= 0)
-          load_packets<Pk<T, CPL>, T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1), &xr[l1 * l1 * NP]);
+        if (kCanon || F.x_off[l1] >= 0)
+          load_packets_scalar<PK, T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1),
+                                              &xr[l1 * l1 * NP]);
       });
     }
 #pragma unroll
@@ -231,138 +393,42 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
       // coupling matrices of this edge, computed while its first unit may still be in flight
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
-      if constexpr (WXW) compute_m_share<T, W == 2>(ell_c, ell_j, ybuf, mbuf, F.m_total, 0, 1, lane);
+      if constexpr (WXW) {
+        if constexpr (kProgramInRegisters) {
+#pragma unroll
+          for (int r = 0; r < kRounds; ++r)
+            mbuf[r * 32 + lane] = fma(prog_b[r], ybuf[prog_j[r] >> 8], prog_a[r] * ybuf[prog_j[r] & 255u]);
+        } else {
+          compute_m_share<T, false>(ell_c, ell_j, ybuf, mbuf, m_total, 0, 1, lane);
+        }
+      }
       if (pos + 1 < p_end && lane < F.Y) y_next = P.y[static_cast<int64_t>(e1) * F.Y + lane];
       __syncwarp();
-      int tile_base = 0;  // first matrix entry held in the reduction tile
-      int tile_end = 0;   // one past the last entry written to the tile
+      tile_base = 0;
+      tile_end = 0;
 
-      // one unit per output degree present; the per-degree arithmetic is selected by a switch so that the wait and
-      // the refill exist once in the loop
-      auto unit_body = [&](auto l3c, const T* unit) {
-        constexpr int l3 = decltype(l3c)::value;
-        constexpr int d3 = 2 * l3 + 1;
-        constexpr int d3p = d3 + 1;
-        V g2[d3 * NP];
-        load_packets<Pk<T, CPL>, T, CPL, d3>(unit + F.ug_soff[l3] + lane * (CPL * d3), g2);
-        static_for<0, LX + 1>([&](auto l1c) {
-          constexpr int l1 = decltype(l1c)::value;
-          constexpr int d1 = 2 * l1 + 1;
-          const int q_end = F.pair_ptr[l3 * L1S + l1 + 1];
-#pragma unroll 1
-          for (int q = F.pair_ptr[l3 * L1S + l1]; q < q_end; ++q) {
-            const int4 rec = ptab[q];
-            const int m_off = rec.y;
-            V w2[NP];  // a lane's consecutive channels are already adjacent in memory
-            load_lane_packets<Pk<T, CPL>, T, CPL>(unit + rec.x + lane * CPL, w2);
-            const V* xl = &xr[l1 * l1 * NP];
-            V* gxl = &gxr[l1 * l1 * NP];
-            // rows go to the tile in chunks that fit it; a chunk that does not fit behind what the tile holds
-            // first reduces that
-            constexpr int rows_per_chunk = (2 * kRedGroups) / d3p < d1 ? (2 * kRedGroups) / d3p : d1;
-            T* tile = nullptr;
-            V dot[NP];
-#pragma unroll
-            for (int p = 0; p < NP; ++p) dot[p] = zero_packet<V>();
-            const T* mrows = mbuf + W * m_off;
-#pragma unroll
-            for (int i = 0; i < d1; ++i) {
-              if (want_y && i % rows_per_chunk == 0) {
-                const int chunk_rows = d1 - i < rows_per_chunk ? d1 - i : rows_per_chunk;
-                const int first = m_off + i * d3p;
-                if (first + chunk_rows * d3p - tile_base > 2 * kRedGroups) {
-                  flush_tile<T>(red, gbuf + tile_base, (tile_end - tile_base) / 2, lane);
-                  tile_base = first;
-                }
-                tile = red + ((first - tile_base) / 2) * red_stride<T>() + lane * 2;
-                tile_end = first + chunk_rows * d3p;
-              }
-              if constexpr (WXW) {
-                V mrow[d3p];
-                load_matrix_row<T, W, d3p, V>(mrows + i * (W * d3p), mrow);
-#pragma unroll
-                for (int p = 0; p < NP; ++p) {
-                  V sv = vmul(mrow[0], g2[p]);
-#pragma unroll
-                  for (int k = 1; k < d3; ++k) sv = vfma(mrow[k], g2[k * NP + p], sv);
-                  gxl[i * NP + p] = vfma(w2[p], sv, gxl[i * NP + p]);
-                  dot[p] = vfma(xl[i * NP + p], sv, dot[p]);
-                }
-              }
-              if (want_y) {
-                V xw[NP];
-#pragma unroll
-                for (int p = 0; p < NP; ++p) xw[p] = vmul(xl[i * NP + p], w2[p]);
-                T grow[d3p];
-#pragma unroll
-                for (int k = 0; k < d3; ++k) {
-                  V acc = vmul(xw[0], g2[k * NP]);
-#pragma unroll
-                  for (int p = 1; p < NP; ++p) acc = vfma(xw[p], g2[k * NP + p], acc);
-                  grow[k] = hsum(acc);
-                }
-                grow[d3] = T(0);
-#pragma unroll
-                for (int kk = 0; kk < d3p / 2; ++kk) {
-                  Vec<T, 2> pr{{grow[2 * kk], grow[2 * kk + 1]}};
-                  *reinterpret_cast<Vec<T, 2>*>(tile + ((i % rows_per_chunk) * (d3p / 2) + kk) * red_stride<T>()) = pr;
-                }
-              }
-            }
-            if (want_w) {
-              T gwv[CPL];
-              unpack_packets<Pk<T, CPL>, T, CPL, 1>(dot, gwv);
-              T* dstw = P.gw + static_cast<int64_t>(e0) * F.W + rec.z + lane * CPL;
-              if (P.acc_w) {
-                T old[CPL];
-                load_vectors<T, CPL, 1>(dstw, old);
-#pragma unroll
-                for (int c = 0; c < CPL; ++c) gwv[c] += old[c];
-              }
-              store_vectors_streaming<T, CPL, 1>(dstw, gwv);
-            }
-          }
+      if constexpr (kCanon) {
+        static_for<0, LO + 1>([&](auto l3c) {
+          if (alive) alive = run_unit(l3c, decltype(l3c)::value);
         });
-      };
+      } else {
+        // the per-degree arithmetic is selected by a switch so that the wait and the refill exist once in the loop
 #pragma unroll 1
-      for (int kind = 0; kind < nk; ++kind) {
-        if (!mbar_wait_bounded(&bars[s], parity)) {
-          if (lane == 0) atomicExch(P.status, 2);
-          alive = false;
-          break;
-        }
-        const T* unit = slots + static_cast<size_t>(s) * slot_elems;
-        switch (F.kind_l3[kind]) {
-          case 0:
-            unit_body(std::integral_constant<int, 0>{}, unit);
-            break;
-          case 1:
-            if constexpr (LO >= 1) unit_body(std::integral_constant<int, 1>{}, unit);
-            break;
-          case 2:
-            if constexpr (LO >= 2) unit_body(std::integral_constant<int, 2>{}, unit);
-            break;
-          default:
-            if constexpr (LO >= 3) unit_body(std::integral_constant<int, 3>{}, unit);
-            break;
-        }
-        __syncwarp();  // every lane is done with this slot
-        if (u + R < total_units) {
-          int next = kind + R, de = 0;
-          if (next >= nk) {
-            next -= nk;
-            de = 1;
+        for (int kind = 0; kind < nk && alive; ++kind) {
+          switch (F.kind_l3[kind]) {
+            case 0:
+              alive = run_unit(std::integral_constant<int, 0>{}, kind);
+              break;
+            case 1:
+              if constexpr (LO >= 1) alive = run_unit(std::integral_constant<int, 1>{}, kind);
+              break;
+            case 2:
+              if constexpr (LO >= 2) alive = run_unit(std::integral_constant<int, 2>{}, kind);
+              break;
+            default:
+              if constexpr (LO >= 3) alive = run_unit(std::integral_constant<int, 3>{}, kind);
+              break;
           }
-          if (next >= nk) {
-            next -= nk;
-            de = 2;
-          }
-          issue(next, de == 0 ? e0 : (de == 1 ? e1 : e2), de == 0 ? d0 : (de == 1 ? d1n : d2n), s);
-        }
-        ++u;
-        if (++s == R) {
-          s = 0;
-          parity ^= 1u;
         }
       }
       if (!alive) break;
@@ -404,7 +470,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
         if (F.x_off[l1] >= 0) {
           T* dstx = P.gx + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1);
           T row[CPL * d1];  // memory order: channel-major, component-minor
-          unpack_packets<Pk<T, CPL>, T, CPL, d1>(&gxr[l1 * l1 * NP], row);
+          unpack_packets<PK, T, CPL, d1>(&gxr[l1 * l1 * NP], row);
           if (P.acc_x) {
             T old[CPL * d1];
             load_vectors<T, CPL, d1>(dstx, old);
@@ -440,7 +506,15 @@ __global__ void reduce_gy_partial(const T* __restrict__ partial, T* __restrict__
 }
 
 
-template <typename T, int CPL, int LX, int LO>
+}  // namespace fastk
+}  // namespace luna
+
+#include "uvu_fast_bwd_sparse.cuh"
+
+namespace luna {
+namespace fastk {
+
+template <typename T, int CPL, int LX, int LO, int L2>
 int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
                         const T* y, const T* w, const T* g, T* gx, bool acc_x, T* gy, bool acc_y, T* gw, bool acc_w,
                         void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
@@ -459,6 +533,8 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.src_rowptr = graph->src_rowptr;
   P.edge_ids = graph->edge_ids_by_src;
   P.tables = dt.bwd_tables;
+  P.sp_c = nullptr;
+  P.sp_j = nullptr;
   P.status = dt.status;
   P.num_src_nodes = graph->num_src_nodes > 0 ? graph->num_src_nodes : graph->num_nodes;
   P.num_edges = graph->num_edges;
@@ -476,30 +552,44 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   }
   if (gx == nullptr && gy == nullptr && gw == nullptr) return LUNA_OK;
   const bool wxw = gx != nullptr || gw != nullptr;
-  // Register budget by shape, through the launch bounds: FP32 with four channels per lane or degree-3 blocks runs up
-  // to 12 warps in a CTA (168 registers), smaller FP32 shapes up to 16 (128 registers); FP64 keeps 8 warps (255).
-  constexpr int MAXW = sizeof(T) == 8 ? 8 : ((CPL == 4 || LX == 3 || LO == 3) ? 12 : 16);
-  constexpr int MINB = 1;
-  auto kernel = gy == nullptr ? fast_bwd_kernel<T, CPL, LX, LO, true, false, MAXW, MINB>
-                              : (wxw ? fast_bwd_kernel<T, CPL, LX, LO, true, true, MAXW, MINB>
-                                     : fast_bwd_kernel<T, CPL, LX, LO, false, true, MAXW, MINB>);
-  cudaFuncAttributes attr;
-  LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
-  // between two units and two edges in a warp's ring
-  const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), bwd_fixed_bytes<T, CPL>(f),
-                                       bwd_shared_bytes(f), dt.max_smem_optin, attr.numRegs, MAXW, 2,
-                                       std::min(kMaxSlots, 2 * f.nkinds));
-  if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
-  P.slots = r.depth;
-  const size_t block_bytes = r.block_bytes;
-  const int nwarps = r.warps;
-  LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
-  // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
-  LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-  const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
-  const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
-  kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
-  LUNA_LAUNCH_CHECK("staged backward");
+  bool launched = false;
+  if constexpr (L2 >= 0) {
+    // compiled-in coupling patterns, if the plan's terms have them
+    if constexpr (sparse_shape_ok<LX, (L2 < 0 ? 0 : L2), LO>()) {
+      if (f.sparse_terms > 0 && std::getenv("LUNA_B200_NO_SPARSE") == nullptr) {
+        const int rc = launch_fast_bwd_sparse<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream);
+        if (rc != LUNA_OK) return rc;
+        launched = true;
+      }
+    }
+  }
+  if (!launched) {
+    // Register budget by shape, through the launch bounds: FP32 with four channels per lane or degree-3 blocks runs
+    // up to 12 warps in a CTA (168 registers), smaller FP32 shapes up to 16 (128 registers); FP64 and the unrolled
+    // canonical kernels keep 8 warps (255).
+    constexpr int MAXW = (sizeof(T) == 8 || L2 >= 0) ? 8 : ((CPL == 4 || LX == 3 || LO == 3) ? 12 : 16);
+    constexpr int MINB = 1;
+    auto kernel = gy == nullptr ? fast_bwd_kernel<T, CPL, LX, LO, L2, true, false, MAXW, MINB>
+                                : (wxw ? fast_bwd_kernel<T, CPL, LX, LO, L2, true, true, MAXW, MINB>
+                                       : fast_bwd_kernel<T, CPL, LX, LO, L2, false, true, MAXW, MINB>);
+    cudaFuncAttributes attr;
+    LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
+    // between two units and two edges in a warp's ring
+    const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), bwd_fixed_bytes<T, CPL>(f),
+                                         bwd_shared_bytes(f), dt.max_smem_optin, attr.numRegs, MAXW, 2,
+                                         std::min(kMaxSlots, 2 * f.nkinds));
+    if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
+    P.slots = r.depth;
+    const size_t block_bytes = r.block_bytes;
+    const int nwarps = r.warps;
+    LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
+    // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
+    LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
+    const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
+    kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
+    LUNA_LAUNCH_CHECK("staged backward");
+  }
   if (P.gy_partial != nullptr) {
     const unsigned rb = static_cast<unsigned>(ceil_div(partial_count, 256));
     reduce_gy_partial<T><<<rb, 256, 0, stream>>>(P.gy_partial, gy, partial_count, f.chunks, acc_y ? 1 : 0);
@@ -512,12 +602,18 @@ template <typename T, int CPL>
 int launch_fast_bwd(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
                     const T* y, const T* w, const T* g, T* gx, bool acc_x, T* gy, bool acc_y, T* gw, bool acc_w,
                     void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
-  const int lx = plan->fast.LX, lo = plan->fast.LO;
+  const int lx = plan->fast.LX, lo = plan->fast.LO, l2 = plan->fast.canon_l2;
 #define LUNA_BWD_ARGS plan, dt, graph, x, y, w, g, gx, acc_x, gy, acc_y, gw, acc_w, scratch, scratch_bytes, stream
-  if (lx <= 1 && lo <= 1) return launch_fast_bwd_one<T, CPL, 1, 1>(LUNA_BWD_ARGS);
-  if (lx <= 2 && lo <= 2) return launch_fast_bwd_one<T, CPL, 2, 2>(LUNA_BWD_ARGS);
-  if (lx <= 2 && lo <= 3) return launch_fast_bwd_one<T, CPL, 2, 3>(LUNA_BWD_ARGS);
-  return launch_fast_bwd_one<T, CPL, 3, 3>(LUNA_BWD_ARGS);
+  if (std::getenv("LUNA_B200_NO_CANON") == nullptr) {
+    if (lx == 2 && l2 == 3 && lo == 3) return launch_fast_bwd_one<T, CPL, 2, 3, 3>(LUNA_BWD_ARGS);
+    if (lx == 2 && l2 == 2 && lo == 2) return launch_fast_bwd_one<T, CPL, 2, 2, 2>(LUNA_BWD_ARGS);
+    if (lx == 3 && l2 == 3 && lo == 3) return launch_fast_bwd_one<T, CPL, 3, 3, 3>(LUNA_BWD_ARGS);
+    if (lx == 1 && l2 == 1 && lo == 1) return launch_fast_bwd_one<T, CPL, 1, 1, 1>(LUNA_BWD_ARGS);
+  }
+  if (lx <= 1 && lo <= 1) return launch_fast_bwd_one<T, CPL, 1, 1, -1>(LUNA_BWD_ARGS);
+  if (lx <= 2 && lo <= 2) return launch_fast_bwd_one<T, CPL, 2, 2, -1>(LUNA_BWD_ARGS);
+  if (lx <= 2 && lo <= 3) return launch_fast_bwd_one<T, CPL, 2, 3, -1>(LUNA_BWD_ARGS);
+  return launch_fast_bwd_one<T, CPL, 3, 3, -1>(LUNA_BWD_ARGS);
 #undef LUNA_BWD_ARGS
 }
 
