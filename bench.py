@@ -135,6 +135,10 @@ class ClockSampler:
                 if value == "Active":
                     self.reasons.add(name)
 
+    def reset(self):
+        """Drop the samples taken so far (warm-up); the timed region starts now."""
+        self.samples, self.reasons = [], set()
+
     def stop(self):
         if self.proc is not None:
             self.proc.terminate()
@@ -274,12 +278,15 @@ def main():
             gx_full = sharded._reduce_scatter_rows(gx_full, world, None)[:atoms]
         return result, gx_full, gy, gw
 
+    # the clock sampler starts before the warm-up: the first nvidia-smi query can stall the device for milliseconds
+    sampler = ClockSampler(device) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(device) if rank == 0 else None
+    if sampler is not None:
+        sampler.reset()
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()

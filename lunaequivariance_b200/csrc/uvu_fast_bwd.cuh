@@ -376,7 +376,8 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
 
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t pe = P.src_rowptr[n + 1];
-    if (pos < pe) {
+    if (pos >= pe) continue;  // no out-edges: the row of gx was zero-filled (or is left as it is) by the launcher
+    {
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         constexpr int d1 = 2 * l1 + 1;
@@ -552,6 +553,10 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   }
   if (gx == nullptr && gy == nullptr && gw == nullptr) return LUNA_OK;
   const bool wxw = gx != nullptr || gw != nullptr;
+  // Source rows without out-edges are skipped by the kernels (a long run of them, as in a destination-range shard,
+  // would otherwise all land on one warp): their rows of gx are zero-filled here.
+  if (gx != nullptr && !acc_x)
+    LUNA_CUDA_CHECK(cudaMemsetAsync(gx, 0, static_cast<size_t>(P.num_src_nodes) * f.X * sizeof(T), stream));
   bool launched = false;
   if constexpr (L2 >= 0) {
     // compiled-in coupling patterns, if the plan's terms have them

@@ -51,8 +51,15 @@ __device__ __forceinline__ void load_four(const T* p, T* out) {
   }
 }
 
+// Warps per CTA at most (caps the registers per thread): FP32 with at most two channels per lane needs fewer
+// registers and runs up to 12 warps (168 registers), everything else 8 (255).
+template <typename T, int CPL>
+__host__ __device__ constexpr int sparse_max_warps() {
+  return (sizeof(T) == 4 && CPL <= 2) ? 12 : 8;
+}
+
 template <typename T, int CPL, int LX, int L2, int LO, bool WXW, bool WY>
-__global__ void __launch_bounds__(256, 1) fast_bwd_sparse_kernel(const __grid_constant__ BwdParams<T> P) {
+__global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_sparse_kernel(const __grid_constant__ BwdParams<T> P) {
   using PK = Pk<T, CPL>;
   using V = typename PK::V;
   constexpr int NP = PK::NP;
@@ -269,7 +276,8 @@ __global__ void __launch_bounds__(256, 1) fast_bwd_sparse_kernel(const __grid_co
 
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t pe = P.src_rowptr[n + 1];
-    if (pos < pe) {
+    if (pos >= pe) continue;  // no out-edges: the row of gx was zero-filled (or is left as it is) by the launcher
+    {
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         constexpr int d1 = 2 * l1 + 1;
@@ -382,7 +390,7 @@ int launch_fast_bwd_sparse(const luna_uvu_plan* plan, const DeviceTables& dt, co
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
   const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), sparse_fixed_bytes<T>(f),
-                                       sparse_shared_bytes<T>(f), dt.max_smem_optin, attr.numRegs, 8, 2,
+                                       sparse_shared_bytes<T>(f), dt.max_smem_optin, attr.numRegs, sparse_max_warps<T, CPL>(), 2,
                                        std::min(kMaxSlots, 2 * f.nkinds));
   if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
   P.slots = r.depth;
