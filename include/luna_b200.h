@@ -88,7 +88,11 @@ typedef enum {
   LUNA_PLAN_CHANNELS_PER_LANE = 1,
   LUNA_PLAN_CHANNEL_CHUNKS = 2,
   LUNA_PLAN_FWD_SMEM_BYTES = 3,
-  LUNA_PLAN_BWD_SMEM_BYTES = 4
+  LUNA_PLAN_BWD_SMEM_BYTES = 4,
+  LUNA_PLAN_CANONICAL_L2 = 5,   /* highest edge-attribute degree if the path list is the full list of allowed
+                                   (l1, l2, l3) couplings in standard order (kernels unrolled at compile time), else -1 */
+  LUNA_PLAN_SPARSE_TERMS = 6    /* > 0 if the plan's coupling terms have the compiled-in non-zero patterns, so the
+                                   backward kernel with per-lane contraction of the edge-attribute gradient applies */
 } luna_plan_query;
 LUNA_API int64_t luna_uvu_plan_query(const luna_uvu_plan* plan, int what);
 

@@ -135,6 +135,16 @@ class LunaTPUVUConv:
     def uses_staged_kernels(self) -> bool:
         return bool(self._plan.query(0))
 
+    @property
+    def canonical_l2(self) -> int:
+        """Highest edge-attribute degree if the path list is the full list of allowed couplings, else -1."""
+        return self._plan.query(5)
+
+    @property
+    def uses_compiled_patterns(self) -> bool:
+        """Whether the backward kernel with compiled-in coupling patterns applies."""
+        return self._plan.query(6) > 0
+
     def force_generic(self, enabled: bool = True) -> None:
         """Route every call through the table-driven kernels (for comparisons and tests)."""
         _native.check(_native.library().luna_uvu_plan_set_generic(self._plan.handle, int(enabled)))

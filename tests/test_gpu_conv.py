@@ -214,3 +214,36 @@ def test_input_validation_errors():
         conv(x, y, w, graph=graph, env=torch.ones(2, device=DEVICE))
     with pytest.raises(RuntimeError, match="CUDA is required"):
         conv(x.cpu(), y.cpu(), w.cpu(), graph=graph)
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+@pytest.mark.parametrize("name", ["cfg2", "cfg5", "cfg4"])
+@pytest.mark.parametrize("knob", ["LUNA_B200_NO_CANON", "LUNA_B200_NO_SPARSE"])
+def test_staged_kernel_variants_match_oracle(name, dtype, knob, monkeypatch):
+    """The canonical configurations through the kernels they do not take by default: loops over run-time path
+    tables (NO_CANON) and the unrolled kernel with dense coupling matrices (NO_SPARSE)."""
+    monkeypatch.setenv(knob, "1")
+    conv = run_case(name, dtype, nodes=37, edges=301, seed=3)
+    assert conv.op.uses_staged_kernels and conv.op.canonical_l2 >= 0
+
+
+def test_backward_skips_source_rows_without_edges():
+    """A block of source rows with no out-edges (as on a destination-range shard) must come back as zeros."""
+    dtype = torch.float32
+    conv, meta = build("cfg5", dtype)
+    generator = torch.Generator().manual_seed(11)
+    nodes, edges = 96, 700
+    src = torch.randint(32, (edges,), generator=generator)  # only the first third of the rows are sources
+    dst = torch.sort(torch.randint(nodes, (edges,), generator=generator))[0]
+    dims = (meta["in1_dim"], meta["in2_dim"], meta["out_dim"], meta["weight_numel"])
+    p = random_problem(dims, nodes, src, dtype, generator)
+    ref = oracle_conv.conv_derivatives(meta, *(p[k].double() for k in ("x", "y", "w")), src, dst, nodes,
+                                       p["g"].double(), None, None, None)
+    graph = conv.create_graph(src.to(DEVICE), dst.to(DEVICE), nodes)
+    x, y, w, g = (p[k].to(DEVICE).requires_grad_(True) for k in ("x", "y", "w", "g"))
+    out = conv(x, y, w, graph=graph)
+    gx, gy, gw = torch.autograd.grad(out, (x, y, w), g)
+    assert_close(gx, ref["gx"], dtype, "gx with empty rows")
+    assert float(gx[32:].abs().max()) == 0.0
+    assert_close(gy, ref["gy"], dtype, "gy")
+    assert_close(gw, ref["gw"], dtype, "gw")

@@ -137,3 +137,20 @@ def test_custom_op_fake_shapes():
 
     desc = SphericalHarmonicsConfig((0, 1, 2), True, "component", torch.float32).descriptor()
     assert torch.ops.lunaeq.spherical_harmonics_forward(v, desc).shape == (7, 9)
+
+
+def test_canonical_path_lists_are_detected_without_gpu():
+    """Full lists of allowed couplings select the kernels unrolled at compile time; anything else does not."""
+    from tests.helpers import config
+
+    expected = {"cfg2": 3, "cfg4": 3, "cfg5": 2, "fixture": 1, "wide": 1, "cfg1": -1, "partial": -1}
+    for name, l2 in expected.items():
+        in1, in2, out, instructions, options = config(name)
+        op = luna.prepare_tensor_product(in1, in2, out, instructions, convolution=True, **options)
+        assert op.uses_staged_kernels, name
+        assert op.canonical_l2 == l2, (name, op.canonical_l2)
+        assert op.uses_compiled_patterns == (l2 >= 0), name
+    # the same couplings in another order are not canonical (weight blocks follow the instruction order)
+    in1, in2, out, instructions, options = config("fixture")
+    shuffled = luna.prepare_tensor_product(in1, in2, out, instructions[::-1], convolution=True)
+    assert shuffled.uses_staged_kernels and shuffled.canonical_l2 == -1
