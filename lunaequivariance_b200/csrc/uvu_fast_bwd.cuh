@@ -230,6 +230,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
 
   constexpr int XR = (LX + 1) * (LX + 1) * NP;
   V xr[XR], gxr[XR];
+  const V ones = runtime_one<V, T>(F.m_terms);  // see settle_packets
   int64_t pos = p_begin;
   int64_t u = 0;  // unit being consumed
   int s = 0;
@@ -322,6 +323,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
     if constexpr (kCanon) {
       constexpr int paths_here = canon_unit_index(LX, L2c, LO, -1, -1, l3);
       load_packets_scalar<PK, T, CPL, d3>(unit + paths_here * chw + lane * (CPL * d3), g2);
+      settle_packets<d3 * NP>(g2, ones);
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         static_for<0, L2c + 1>([&](auto l2c) {
@@ -334,6 +336,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
       });
     } else {
       load_packets_scalar<PK, T, CPL, d3>(unit + F.ug_soff[l3] + lane * (CPL * d3), g2);
+      settle_packets<d3 * NP>(g2, ones);
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         const int q_end = F.pair_ptr[l3 * L1S + l1 + 1];
@@ -385,6 +388,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) fast_bwd_kernel(const __grid_
           load_packets_scalar<PK, T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1),
                                               &xr[l1 * l1 * NP]);
       });
+      settle_packets<XR>(xr, ones);
     }
 #pragma unroll
     for (int a = 0; a < XR; ++a) gxr[a] = zero_packet<V>();

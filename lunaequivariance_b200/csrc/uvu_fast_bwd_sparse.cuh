@@ -1,9 +1,18 @@
 // Staged source-major kernel for canonical full path lists, with the coupling tensors' non-zero patterns compiled in
 // (cg_patterns.h): first derivatives gx, gy, gw in one pass over the weights.
 //
-// Work assignment, the ring of (edge, output degree) units and the bulk copies are those of fast_bwd_kernel.  What
-// differs is the arithmetic.  With the pattern of C^p known at compile time, a path is a straight line of packed
-// FMAs over its terms t = (i, j, k), in (i, k, j) order:
+// Work assignment is that of fast_bwd_kernel (a warp owns a range of source nodes and walks their out-edges).
+//
+// Data movement.  DRAM is used well only with large contiguous requests, so an edge's whole weight row comes in
+// with one bulk copy into one of the warp's two row stages, the weight gradients of the edge are written over the
+// weights in that stage (every lane overwrites exactly the words it has read) and the row goes back to gw with one
+// bulk store; the stage is refilled once the store has read it.  Row copies carry an evict-first L2 hint.  The
+// gathered g[dst] row is cut into one block per output degree; these go through a small ring of slots with the
+// default L2 priority (an evict-last hint was measured to hurt: the rows of a large graph then crowd each other
+// and the next kernel out of L2).
+//
+// Arithmetic.  With the pattern of C^p known at compile time, a path is a straight line of packed FMAs over its
+// terms t = (i, j, k), in (i, k, j) order:
 //     s_i   += (c_t y_j) * g_k                         the per-edge scalars c_t y_j come from a small program
 //     gx_i  += w_p * s_i,   gw_p += x_i * s_i           at the end of row i
 //     P_ik   = sum over the lane's channels of (x_i w_p) * g_k      once per distinct (i, k)
@@ -21,18 +30,24 @@ namespace luna {
 namespace fastk {
 
 constexpr int kMaxSparseRounds = 16;  // program entries a lane keeps in registers (two registers each)
+constexpr int kSparseTileRows = 8;    // reduction tile: one pair of gy entries per row (in2_dim <= 16)
 
 template <typename T>
 __host__ __device__ inline size_t sparse_fixed_bytes(const FastMeta& f) {
-  // per-edge scalars c_t y_j, reduction tile, reduced gy row, y row, barriers
-  const size_t elems = static_cast<size_t>(f.sparse_terms + 31) / 32 * 32 +
-                       static_cast<size_t>(kRedGroups) * red_stride<T>() + 32 + 32;
-  return elems * sizeof(T) + kMaxSlots * sizeof(uint64_t);
+  // two weight-row stages, per-edge scalars c_t y_j, reduction tile, reduced gy row, y row, barriers
+  const size_t elems = 2 * static_cast<size_t>(f.w_stage_elems) + static_cast<size_t>(f.sparse_terms + 31) / 32 * 32 +
+                       static_cast<size_t>(kSparseTileRows) * red_stride<T>() + 32 + 32;
+  return elems * sizeof(T) + (2 + kMaxSlots) * sizeof(uint64_t);
 }
-// Per-CTA shared tables: the term coefficients plus one record per path.
+// One slot of the g ring: the widest degree block of the row.
+template <typename T>
+__host__ __device__ inline size_t sparse_slot_bytes(const FastMeta& f) {
+  return static_cast<size_t>(32 * f.cpl) * (2 * f.LO + 1) * sizeof(T);
+}
+// Per-CTA shared tables: the term coefficients.
 template <typename T>
 __host__ __device__ inline size_t sparse_shared_bytes(const FastMeta& f) {
-  return static_cast<size_t>(f.sparse_terms) * sizeof(T) + kMaxFastPaths * sizeof(int4);
+  return (static_cast<size_t>(f.sparse_terms) * sizeof(T) + 127) / 128 * 128;
 }
 
 // Four consecutive entries of a 16-byte aligned table; every lane reads the same address.
@@ -51,6 +66,36 @@ __device__ __forceinline__ void load_four(const T* p, T* out) {
   }
 }
 
+// Adds the 32 lane contributions of tile rows [0, ROWS) (row r holds the lanes' values of entries 2r and 2r + 1,
+// interleaved) and writes the sums to out[0 .. 2 * ROWS).  Four lanes share a row, a quarter each.
+template <typename T, int ROWS>
+__device__ __forceinline__ void reduce_tile_rows(const T* red, T* out, int lane) {
+  static_assert(ROWS <= kSparseTileRows, "tile too small");
+  __syncwarp();
+  constexpr int per = 16 / static_cast<int>(sizeof(T));
+  const int r = lane & 7, part = lane >> 3;
+  const T* seg = red + r * red_stride<T>() + part * 16;
+  T s0 = T(0), s1 = T(0);
+#pragma unroll
+  for (int v = 0; v < 16 / per; ++v) {
+    const Vec<T, per> q = reinterpret_cast<const Vec<T, per>*>(seg)[v];
+#pragma unroll
+    for (int c = 0; c < per; c += 2) {
+      s0 += q.a[c];
+      s1 += q.a[c + 1];
+    }
+  }
+  s0 += __shfl_xor_sync(0xffffffffu, s0, 8);
+  s1 += __shfl_xor_sync(0xffffffffu, s1, 8);
+  s0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+  s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+  if (lane < ROWS) {
+    Vec<T, 2> pr{{s0, s1}};
+    reinterpret_cast<Vec<T, 2>*>(out)[lane] = pr;
+  }
+  __syncwarp();
+}
+
 // Warps per CTA at most (caps the registers per thread): FP32 with at most two channels per lane needs fewer
 // registers and runs up to 12 warps (168 registers), everything else 8 (255).
 template <typename T, int CPL>
@@ -63,50 +108,54 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
   using PK = Pk<T, CPL>;
   using V = typename PK::V;
   constexpr int NP = PK::NP;
-  constexpr int L1S = kMaxFastL + 1;
   constexpr int TT = canon_toff(LX, L2, LO, -1, -1, -1);  // terms, padded per path
   constexpr int kRounds = (TT + 31) / 32;
   static_assert(kRounds <= kMaxSparseRounds, "coupling program too long for the register budget");
   constexpr int YD = (L2 + 1) * (L2 + 1);
+  static_assert((YD + 1) / 2 <= kSparseTileRows, "edge attributes too wide for the reduction tile");
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const FastMeta& F = P.meta;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int R = P.slots;
+  const int R = P.slots;  // slots of the g ring
   constexpr int nk = LO + 1;
-  const int slot_elems = F.slot_elems;
   constexpr int chw = 32 * CPL;
+  constexpr int gslot_elems = chw * (2 * LO + 1);
   const int c0 = blockIdx.y * chw;
+  const int wrow_elems = F.w_stage_elems;
 
-  // CTA-wide tables: term coefficients, and per path the global w offset for this CTA's channels
+  // CTA-wide table: term coefficients
   T* ctab = reinterpret_cast<T*>(smem_raw);
   for (int i = threadIdx.x; i < TT; i += blockDim.x) ctab[i] = P.sp_c[i];
-  int4* ptab = reinterpret_cast<int4*>(smem_raw + static_cast<size_t>(TT) * sizeof(T));
-  for (int q = threadIdx.x; q < F.num_paths; q += blockDim.x)
-    ptab[q] = make_int4(F.uw_soff[q], F.m_off[q], F.w_goff[q] + c0, 0);
   __syncthreads();
 
-  const size_t warp_bytes = static_cast<size_t>(R) * slot_elems * sizeof(T) + sparse_fixed_bytes<T>(F);
-  T* slots = reinterpret_cast<T*>(smem_raw + sparse_shared_bytes<T>(F) + static_cast<size_t>(warp) * warp_bytes);
-  T* cybuf = slots + static_cast<size_t>(R) * slot_elems;
+  const size_t warp_bytes = static_cast<size_t>(R) * gslot_elems * sizeof(T) + sparse_fixed_bytes<T>(F);
+  T* wst = reinterpret_cast<T*>(smem_raw + sparse_shared_bytes<T>(F) + static_cast<size_t>(warp) * warp_bytes);
+  T* gsl = wst + 2 * static_cast<size_t>(wrow_elems);
+  T* cybuf = gsl + static_cast<size_t>(R) * gslot_elems;
   T* red = cybuf + (TT + 31) / 32 * 32;
-  T* gbuf = red + kRedGroups * red_stride<T>();
+  T* gbuf = red + kSparseTileRows * red_stride<T>();
   T* ybuf = gbuf + 32;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ybuf + 32);
+  uint64_t* wbar = reinterpret_cast<uint64_t*>(ybuf + 32);
+  uint64_t* gbar = wbar + 2;
 
   if (lane == 0) {
-    for (int s = 0; s < R; ++s) mbar_init(&bars[s], 1);
+    mbar_init(&wbar[0], 1);
+    mbar_init(&wbar[1], 1);
+    for (int s = 0; s < R; ++s) mbar_init(&gbar[s], 1);
     fence_barrier_init();
   }
   __syncwarp();
 
   // the lane's share of the per-edge program cy[t] = c_t * y[j_t]: entries lane, lane + 32, ...
   T prog_c[kRounds];
-  unsigned prog_j[kRounds];
+  unsigned prog_j[(kRounds + 3) / 4];  // four 8-bit y indices per register
+#pragma unroll
+  for (int r = 0; r < (kRounds + 3) / 4; ++r) prog_j[r] = 0u;
 #pragma unroll
   for (int r = 0; r < kRounds; ++r) {
     const int t = r * 32 + lane;
     prog_c[r] = t < TT ? ctab[t] : T(0);
-    prog_j[r] = t < TT ? P.sp_j[t] : 0u;
+    prog_j[r / 4] |= (t < TT ? static_cast<unsigned>(P.sp_j[t]) : 0u) << (8 * (r % 4));
   }
 
   const int64_t E = P.num_edges, N = P.num_src_nodes;
@@ -119,21 +168,39 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
   if (n_lo >= n_hi) return;
   const int64_t p_begin = P.src_rowptr[n_lo], p_end = P.src_rowptr[n_hi];
   const bool want_x = WXW && P.gx != nullptr, want_w = WXW && P.gw != nullptr;
+  const bool stage_gw = want_w && !P.acc_w;  // gradients overwrite the weights in the stage and leave as a row
   const int64_t total_units = (p_end - p_begin) * nk;
 
-  // Lane L copies the w chunk of the unit's L-th path; the lane after the last path copies the g block.
-  auto issue = [&](int l3, int64_t e, int64_t d_node, int s) {
-    uint64_t* bar = &bars[s];
-    const int q0 = F.pair_ptr[l3 * L1S], np = F.pair_ptr[l3 * L1S + L1S] - q0;
-    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(F.unit_elems[l3] * sizeof(T)));
+  // Weight rows: lane L moves piece L of the row (one piece when the row is contiguous for this CTA's channels).
+  const int n_wp = F.n_w_pieces;
+  auto load_row = [&](int64_t e, int st) {
+    if (lane == 0) mbar_arrive_expect_tx(&wbar[st], static_cast<uint32_t>(wrow_elems * sizeof(T)));
     __syncwarp();
-    T* to = slots + static_cast<size_t>(s) * slot_elems;
-    if (lane < np) {
-      bulk_copy_g2s(to + lane * chw, P.w + e * F.W + ptab[q0 + lane].z, static_cast<uint32_t>(chw * sizeof(T)), bar);
-    } else if (lane == np) {
-      const int d3 = 2 * l3 + 1;
-      bulk_copy_g2s(to + np * chw, P.g + d_node * F.O + F.o_off[l3] + c0 * d3,
-                    static_cast<uint32_t>(chw * d3 * sizeof(T)), bar);
+    if (lane < n_wp) {
+      const CopyPiece pc = F.pieces_w[lane];
+      bulk_copy_g2s_hint(wst + static_cast<size_t>(st) * wrow_elems + pc.s_off,
+                         P.w + e * F.W + pc.g_off + static_cast<int64_t>(c0) * pc.comp,
+                         static_cast<uint32_t>(pc.n * sizeof(T)), &wbar[st], l2_policy_evict_first());
+    }
+  };
+  auto store_row = [&](int64_t e, int st) {
+    fence_async_shared();  // the lanes' gradient writes, before the bulk store reads the stage
+    __syncwarp();
+    if (lane < n_wp) {
+      const CopyPiece pc = F.pieces_w[lane];
+      bulk_copy_s2g_hint(P.gw + e * F.W + pc.g_off + static_cast<int64_t>(c0) * pc.comp,
+                         wst + static_cast<size_t>(st) * wrow_elems + pc.s_off, static_cast<uint32_t>(pc.n * sizeof(T)),
+                         l2_policy_evict_first());
+      bulk_commit_group();
+    }
+  };
+  // g ring: one block of the destination's row per unit
+  auto load_g = [&](int l3, int64_t d_node, int s) {
+    const int d3 = 2 * l3 + 1;
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&gbar[s], static_cast<uint32_t>(chw * d3 * sizeof(T)));
+      bulk_copy_g2s(gsl + static_cast<size_t>(s) * gslot_elems, P.g + d_node * F.O + F.o_off[l3] + c0 * d3,
+                    static_cast<uint32_t>(chw * d3 * sizeof(T)), &gbar[s]);
     }
   };
 
@@ -143,23 +210,31 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
   auto dst_of = [&](int e) { return e >= 0 ? P.dst[e] : 0; };
   int e0 = id_at(p_begin), e1 = id_at(p_begin + 1), e2 = id_at(p_begin + 2), e3 = id_at(p_begin + 3);
   int d0 = dst_of(e0), d1n = dst_of(e1), d2n = dst_of(e2);
+  load_row(e0, 0);
+  if (e1 >= 0) load_row(e1, 1);
   for (int v = 0; v < R && v < total_units; ++v) {
     const int de = v / nk, kind = v - de * nk;  // R <= 2 * nk, so de is 0 or 1
-    issue(kind, de == 0 ? e0 : e1, de == 0 ? d0 : d1n, v);
+    load_g(kind, de == 0 ? d0 : d1n, v);
   }
   T y_next = (lane < F.Y && e0 >= 0) ? P.y[static_cast<int64_t>(e0) * F.Y + lane] : T(0);
 
   constexpr int XR = (LX + 1) * (LX + 1) * NP;
   V xr[XR], gxr[XR];
+  const V ones = runtime_one<V, T>(F.m_terms);
   V gy2[WY ? YD : 1];
   int64_t pos = p_begin;
   int64_t u = 0;  // unit being consumed
-  int s = 0;
-  uint32_t parity = 0;
+  int s = 0;      // its slot in the g ring
+  uint32_t gparity = 0;
+  int st = 0;  // row stage of the current edge
+  uint32_t wparity = 0;  // bit s: parity of stage s
   bool alive = true;
+  bool store_pending = false;  // the other stage has a row store in flight and is to be refilled after it
+  bool first_edge = true;
 
-  // One path: a straight line over its coupling terms.
-  auto path_body = [&](auto l1c, auto l2c, auto l3c, const V* g2, const T* wq, int64_t w_goff) {
+  // One path: a straight line over its coupling terms.  wq: the lane's weights in the row stage (overwritten with
+  // their gradients when the row is staged back); w_goff: their global offset.
+  auto path_body = [&](auto l1c, auto l2c, auto l3c, const V* g2, T* wq, int64_t w_goff) {
     constexpr int l1 = decltype(l1c)::value, l2 = decltype(l2c)::value, l3 = decltype(l3c)::value;
     using PT = CgPattern<l1, l2, l3>;
     constexpr int n = PT::n;
@@ -215,44 +290,46 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
     if (want_w) {
       T gwv[CPL];
       unpack_packets<PK, T, CPL, 1>(dot, gwv);
-      T* dstw = P.gw + w_goff;
-      if (P.acc_w) {
+      if (stage_gw) {
+        store_vectors<T, CPL, 1>(wq, gwv);
+      } else {
+        T* dstw = P.gw + w_goff;
         T old[CPL];
         load_vectors<T, CPL, 1>(dstw, old);
 #pragma unroll
         for (int c = 0; c < CPL; ++c) gwv[c] += old[c];
+        store_vectors_streaming<T, CPL, 1>(dstw, gwv);
       }
-      store_vectors_streaming<T, CPL, 1>(dstw, gwv);
     }
   };
 
   // One unit = the paths into output degree l3 of the current edge.
-  auto unit_body = [&](auto l3c, const T* unit) {
+  auto unit_body = [&](auto l3c, const T* gblock, T* wrow) {
     constexpr int l3 = decltype(l3c)::value;
     constexpr int d3 = 2 * l3 + 1;
-    constexpr int paths_here = canon_unit_index(LX, L2, LO, -1, -1, l3);
     V g2[d3 * NP];
-    load_packets_scalar<PK, T, CPL, d3>(unit + paths_here * chw + lane * (CPL * d3), g2);
+    load_packets_scalar<PK, T, CPL, d3>(gblock + lane * (CPL * d3), g2);
+    settle_packets<d3 * NP>(g2, ones);
     const int64_t w_row = static_cast<int64_t>(e0) * F.W + lane * CPL + c0;
     static_for<0, LX + 1>([&](auto l1c) {
       constexpr int l1 = decltype(l1c)::value;
       static_for<0, L2 + 1>([&](auto l2c) {
         constexpr int l2 = decltype(l2c)::value;
         if constexpr (canon_ok(LX, L2, LO, l1, l2, l3))
-          path_body(l1c, l2c, l3c, g2, unit + canon_unit_index(LX, L2, LO, l1, l2, l3) * chw + lane * CPL,
+          path_body(l1c, l2c, l3c, g2, wrow + canon_wrank(LX, L2, LO, l1, l2, l3) * chw + lane * CPL,
                     w_row + canon_wrank(LX, L2, LO, l1, l2, l3) * F.ch);
       });
     });
   };
 
-  // waits for the unit in slot s, runs it and refills the slot with the unit R places later
-  auto run_unit = [&](auto l3c) -> bool {
+  // waits for the unit's g block, runs the unit and refills the slot with the block R units later
+  auto run_unit = [&](auto l3c, T* wrow) -> bool {
     constexpr int kind = decltype(l3c)::value;
-    if (!mbar_wait_bounded(&bars[s], parity)) {
+    if (!mbar_wait_bounded(&gbar[s], gparity)) {
       if (lane == 0) atomicExch(P.status, 2);
       return false;
     }
-    unit_body(l3c, slots + static_cast<size_t>(s) * slot_elems);
+    unit_body(l3c, gsl + static_cast<size_t>(s) * gslot_elems, wrow);
     __syncwarp();  // every lane is done with this slot
     if (u + R < total_units) {
       int next = kind + R, de = 0;
@@ -264,12 +341,12 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
         next -= nk;
         de = 2;
       }
-      issue(next, de == 0 ? e0 : (de == 1 ? e1 : e2), de == 0 ? d0 : (de == 1 ? d1n : d2n), s);
+      load_g(next, de == 0 ? d0 : (de == 1 ? d1n : d2n), s);
     }
     ++u;
     if (++s == R) {
       s = 0;
-      parity ^= 1u;
+      gparity ^= 1u;
     }
     return true;
   };
@@ -284,18 +361,20 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
         load_packets_scalar<PK, T, CPL, d1>(P.x + n * F.X + F.x_off[l1] + c0 * d1 + lane * (CPL * d1),
                                             &xr[l1 * l1 * NP]);
       });
+      settle_packets<XR>(xr, ones);
     }
 #pragma unroll
     for (int a = 0; a < XR; ++a) gxr[a] = zero_packet<V>();
 
 #pragma unroll 1
     for (; pos < pe && alive; ++pos) {
-      // per-edge scalars, computed while the edge's first unit may still be in flight
+      // per-edge scalars, computed while the edge's row may still be in flight
       if (lane < F.Y) ybuf[lane] = y_next;
       __syncwarp();
       if constexpr (WXW) {
 #pragma unroll
-        for (int r = 0; r < kRounds; ++r) cybuf[r * 32 + lane] = prog_c[r] * ybuf[prog_j[r]];
+        for (int r = 0; r < kRounds; ++r)
+          cybuf[r * 32 + lane] = prog_c[r] * ybuf[(prog_j[r / 4] >> (8 * (r % 4))) & 255u];
       }
       if (pos + 1 < p_end && lane < F.Y) y_next = P.y[static_cast<int64_t>(e1) * F.Y + lane];
       __syncwarp();
@@ -304,10 +383,34 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
         for (int j = 0; j < YD; ++j) gy2[j] = zero_packet<V>();
       }
 
+      // the edge's weight row
+      if (!mbar_wait_bounded(&wbar[st], (wparity >> st) & 1u)) {
+        if (lane == 0) atomicExch(P.status, 3);
+        alive = false;
+        break;
+      }
+      wparity ^= 1u << st;
+      T* wrow = wst + static_cast<size_t>(st) * wrow_elems;
+
       static_for<0, LO + 1>([&](auto l3c) {
-        if (alive) alive = run_unit(l3c);
+        if (alive) alive = run_unit(l3c, wrow);
+        if constexpr (decltype(l3c)::value == 0) {
+          // the other stage: once the previous edge's row store has read it, fetch the next edge's row into it
+          if (store_pending) {
+            if (lane < n_wp) bulk_wait_group_read_all();
+            __syncwarp();
+            store_pending = false;
+          }
+          if (!first_edge && pos + 1 < p_end) load_row(e1, st ^ 1);
+          first_edge = false;
+        }
       });
       if (!alive) break;
+
+      if (stage_gw) {
+        store_row(e0, st);
+        store_pending = true;
+      }
 
       if constexpr (WY) {
         // the lane's partial gy row goes through the reduction tile: entry pair r in row r
@@ -322,7 +425,7 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
           }
           *reinterpret_cast<Vec<T, 2>*>(red + r * red_stride<T>() + lane * 2) = pr;
         });
-        flush_tile<T>(red, gbuf, (YD + 1) / 2, lane);
+        reduce_tile_rows<T, (YD + 1) / 2>(red, gbuf, lane);
         if (lane < F.Y) {
           const T acc = lane < YD ? gbuf[lane] : T(0);
           if (P.gy_partial != nullptr) {
@@ -341,6 +444,7 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
       e2 = e3;
       if (pos + 3 < p_end) d2n = P.dst[e2];
       if (pos + 4 < p_end) e3 = P.edge_ids[pos + 4];
+      st ^= 1;
     }
     if (!alive) break;
     if (want_x) {
@@ -360,22 +464,26 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
       });
     }
   }
-  if (!alive) {  // let copies that are still in flight land before the CTA's shared memory is released
+  // row stores must have read their stages before the CTA's shared memory is released
+  if (lane < n_wp) bulk_wait_group_read_all();
+  if (!alive) {  // let copies that are still in flight land as well (bounded)
     const int64_t last = u + R < total_units ? u + R : total_units;
     for (int64_t v = u + 1; v < last; ++v) {
       if (++s == R) {
         s = 0;
-        parity ^= 1u;
+        gparity ^= 1u;
       }
-      mbar_wait_bounded(&bars[s], parity);
+      mbar_wait_bounded(&gbar[s], gparity);
     }
+    mbar_wait_bounded(&wbar[0], wparity & 1u);
+    mbar_wait_bounded(&wbar[1], (wparity >> 1) & 1u);
   }
 }
 
 // Whether the compiled-in program length fits this shape (checked at compile time per instantiation).
 template <int LX, int L2, int LO>
 constexpr bool sparse_shape_ok() {
-  return (canon_toff(LX, L2, LO, -1, -1, -1) + 31) / 32 <= kMaxSparseRounds;
+  return (canon_toff(LX, L2, LO, -1, -1, -1) + 31) / 32 <= kMaxSparseRounds && (L2 + 1) * (L2 + 1) <= 2 * kSparseTileRows;
 }
 
 template <typename T, int CPL, int LX, int L2, int LO>
@@ -389,9 +497,9 @@ int launch_fast_bwd_sparse(const luna_uvu_plan* plan, const DeviceTables& dt, co
                                : fast_bwd_sparse_kernel<T, CPL, LX, L2, LO, false, true>);
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
-  const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), sparse_fixed_bytes<T>(f),
-                                       sparse_shared_bytes<T>(f), dt.max_smem_optin, attr.numRegs, sparse_max_warps<T, CPL>(), 2,
-                                       std::min(kMaxSlots, 2 * f.nkinds));
+  const Residency r = choose_residency(sparse_slot_bytes<T>(f), sparse_fixed_bytes<T>(f), sparse_shared_bytes<T>(f),
+                                       dt.max_smem_optin, attr.numRegs, sparse_max_warps<T, CPL>(), 2,
+                                       std::min(4, 2 * f.nkinds));
   if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
   P.slots = r.depth;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(r.block_bytes)));

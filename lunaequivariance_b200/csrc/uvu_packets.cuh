@@ -210,5 +210,22 @@ __device__ __forceinline__ void load_plain_row(const T* matrix, T* row) {
     }
   });
 }
+
+// A pair that was only assembled from two scalars (mov.b64 {lo, hi}) is not a value of its own for the assembler:
+// under register pressure it keeps the halves apart and re-assembles the pair in front of every packed instruction
+// that uses it, which costs more moves than arithmetic.  A pair that has gone through one arithmetic instruction
+// stays in one 64-bit register.  settle_packets multiplies freshly assembled pairs by a 1.0 the compiler cannot see
+// through (derived from a kernel parameter that always holds 2); for scalar packets it does nothing.
+template <typename V, typename T>
+__device__ __forceinline__ V runtime_one(int two) {
+  return bcast_packet(static_cast<T>(two) * T(0.5), V{});
+}
+template <int N>
+__device__ __forceinline__ void settle_packets(Pair* v, Pair one) {
+#pragma unroll
+  for (int a = 0; a < N; ++a) v[a] = vmul(v[a], one);
+}
+template <int N, typename S>
+__device__ __forceinline__ void settle_packets(S*, S) {}
 }  // namespace fastk
 }  // namespace luna
