@@ -55,6 +55,7 @@ struct BwdParams {
   int* status;
   int64_t num_src_nodes, num_edges;
   int slots;
+  int row_stages;  // kernel with compiled-in patterns: weight-row stages per warp
   int acc_x, acc_y, acc_w;
 };
 
@@ -515,6 +516,7 @@ __global__ void reduce_gy_partial(const T* __restrict__ partial, T* __restrict__
 }  // namespace luna
 
 #include "uvu_fast_bwd_sparse.cuh"
+#include "uvu_fast_bwd_units.cuh"
 
 namespace luna {
 namespace fastk {
@@ -540,6 +542,7 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.tables = dt.bwd_tables;
   P.sp_c = nullptr;
   P.sp_j = nullptr;
+  P.row_stages = 0;
   P.status = dt.status;
   P.num_src_nodes = graph->num_src_nodes > 0 ? graph->num_src_nodes : graph->num_nodes;
   P.num_edges = graph->num_edges;
@@ -566,7 +569,12 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     // compiled-in coupling patterns, if the plan's terms have them
     if constexpr (sparse_shape_ok<LX, (L2 < 0 ? 0 : L2), LO>()) {
       if (f.sparse_terms > 0 && std::getenv("LUNA_B200_NO_SPARSE") == nullptr) {
-        const int rc = launch_fast_bwd_sparse<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream);
+        // Row stages pay off when an edge's weight row is one long contiguous piece for this CTA; short rows and
+        // rows split into channel chunks go through the unit ring (LUNA_B200_BWD_KERNEL=row|units overrides).
+        bool rows = f.chunks == 1 && static_cast<size_t>(f.w_stage_elems) * sizeof(T) >= 2560;
+        if (const char* knob = std::getenv("LUNA_B200_BWD_KERNEL")) rows = knob[0] == 'r';
+        const int rc = rows ? launch_fast_bwd_sparse<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream)
+                            : launch_fast_bwd_units<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream);
         if (rc != LUNA_OK) return rc;
         launched = true;
       }

@@ -4,7 +4,7 @@
 // Work assignment is that of fast_bwd_kernel (a warp owns a range of source nodes and walks their out-edges).
 //
 // Data movement.  DRAM is used well only with large contiguous requests, so an edge's whole weight row comes in
-// with one bulk copy into one of the warp's two row stages, the weight gradients of the edge are written over the
+// with one bulk copy into one of the warp's two to four row stages, the weight gradients of the edge are written over the
 // weights in that stage (every lane overwrites exactly the words it has read) and the row goes back to gw with one
 // bulk store; the stage is refilled once the store has read it.  Row copies carry an evict-first L2 hint.  The
 // gathered g[dst] row is cut into one block per output degree; these go through a small ring of slots with the
@@ -31,13 +31,15 @@ namespace fastk {
 
 constexpr int kMaxSparseRounds = 16;  // program entries a lane keeps in registers (two registers each)
 constexpr int kSparseTileRows = 8;    // reduction tile: one pair of gy entries per row (in2_dim <= 16)
+constexpr int kMaxRowStages = 4;      // weight-row stages per warp (the edge ids of four edges are kept ahead)
 
 template <typename T>
-__host__ __device__ inline size_t sparse_fixed_bytes(const FastMeta& f) {
-  // two weight-row stages, per-edge scalars c_t y_j, reduction tile, reduced gy row, y row, barriers
-  const size_t elems = 2 * static_cast<size_t>(f.w_stage_elems) + static_cast<size_t>(f.sparse_terms + 31) / 32 * 32 +
+__host__ __device__ inline size_t sparse_fixed_bytes(const FastMeta& f, int row_stages) {
+  // weight-row stages, per-edge scalars c_t y_j, reduction tile, reduced gy row, y row, barriers
+  const size_t elems = static_cast<size_t>(row_stages) * f.w_stage_elems +
+                       static_cast<size_t>(f.sparse_terms + 31) / 32 * 32 +
                        static_cast<size_t>(kSparseTileRows) * red_stride<T>() + 32 + 32;
-  return elems * sizeof(T) + (2 + kMaxSlots) * sizeof(uint64_t);
+  return elems * sizeof(T) + (kMaxRowStages + kMaxSlots) * sizeof(uint64_t);
 }
 // One slot of the g ring: the widest degree block of the row.
 template <typename T>
@@ -128,19 +130,19 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
   for (int i = threadIdx.x; i < TT; i += blockDim.x) ctab[i] = P.sp_c[i];
   __syncthreads();
 
-  const size_t warp_bytes = static_cast<size_t>(R) * gslot_elems * sizeof(T) + sparse_fixed_bytes<T>(F);
+  const int S = P.row_stages;  // weight-row stages
+  const size_t warp_bytes = static_cast<size_t>(R) * gslot_elems * sizeof(T) + sparse_fixed_bytes<T>(F, S);
   T* wst = reinterpret_cast<T*>(smem_raw + sparse_shared_bytes<T>(F) + static_cast<size_t>(warp) * warp_bytes);
-  T* gsl = wst + 2 * static_cast<size_t>(wrow_elems);
+  T* gsl = wst + static_cast<size_t>(S) * wrow_elems;
   T* cybuf = gsl + static_cast<size_t>(R) * gslot_elems;
   T* red = cybuf + (TT + 31) / 32 * 32;
   T* gbuf = red + kSparseTileRows * red_stride<T>();
   T* ybuf = gbuf + 32;
   uint64_t* wbar = reinterpret_cast<uint64_t*>(ybuf + 32);
-  uint64_t* gbar = wbar + 2;
+  uint64_t* gbar = wbar + kMaxRowStages;
 
   if (lane == 0) {
-    mbar_init(&wbar[0], 1);
-    mbar_init(&wbar[1], 1);
+    for (int s = 0; s < S; ++s) mbar_init(&wbar[s], 1);
     for (int s = 0; s < R; ++s) mbar_init(&gbar[s], 1);
     fence_barrier_init();
   }
@@ -212,6 +214,8 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
   int d0 = dst_of(e0), d1n = dst_of(e1), d2n = dst_of(e2);
   load_row(e0, 0);
   if (e1 >= 0) load_row(e1, 1);
+  if (S > 2 && e2 >= 0) load_row(e2, 2);
+  if (S > 3 && e3 >= 0) load_row(e3, 3);
   for (int v = 0; v < R && v < total_units; ++v) {
     const int de = v / nk, kind = v - de * nk;  // R <= 2 * nk, so de is 0 or 1
     load_g(kind, de == 0 ? d0 : d1n, v);
@@ -229,7 +233,7 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
   int st = 0;  // row stage of the current edge
   uint32_t wparity = 0;  // bit s: parity of stage s
   bool alive = true;
-  bool store_pending = false;  // the other stage has a row store in flight and is to be refilled after it
+  bool store_pending = false;  // the previous edge's stage has a row store in flight; it is refilled after that
   bool first_edge = true;
 
   // One path: a straight line over its coupling terms.  wq: the lane's weights in the row stage (overwritten with
@@ -401,7 +405,9 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
             __syncwarp();
             store_pending = false;
           }
-          if (!first_edge && pos + 1 < p_end) load_row(e1, st ^ 1);
+          // the row S - 1 edges ahead goes into the stage the previous edge has just left
+          if (!first_edge && pos + S - 1 < p_end)
+            load_row(S == 2 ? e1 : (S == 3 ? e2 : e3), st == 0 ? S - 1 : st - 1);
           first_edge = false;
         }
       });
@@ -444,7 +450,7 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
       e2 = e3;
       if (pos + 3 < p_end) d2n = P.dst[e2];
       if (pos + 4 < p_end) e3 = P.edge_ids[pos + 4];
-      st ^= 1;
+      if (++st == S) st = 0;
     }
     if (!alive) break;
     if (want_x) {
@@ -475,8 +481,7 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_s
       }
       mbar_wait_bounded(&gbar[s], gparity);
     }
-    mbar_wait_bounded(&wbar[0], wparity & 1u);
-    mbar_wait_bounded(&wbar[1], (wparity >> 1) & 1u);
+    for (int v = 0; v < S; ++v) mbar_wait_bounded(&wbar[v], (wparity >> v) & 1u);
   }
 }
 
@@ -497,11 +502,32 @@ int launch_fast_bwd_sparse(const luna_uvu_plan* plan, const DeviceTables& dt, co
                                : fast_bwd_sparse_kernel<T, CPL, LX, L2, LO, false, true>);
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
-  const Residency r = choose_residency(sparse_slot_bytes<T>(f), sparse_fixed_bytes<T>(f), sparse_shared_bytes<T>(f),
-                                       dt.max_smem_optin, attr.numRegs, sparse_max_warps<T, CPL>(), 2,
-                                       std::min(4, 2 * f.nkinds));
+  // One CTA per SM.  As many warps as registers and shared memory allow, then as many row stages as fit (up to
+  // four: short rows need the deeper prefetch), then a deeper g ring.
+  Residency r;
+  int row_stages = 0;
+  {
+    int max_warps = std::min(sparse_max_warps<T, CPL>(), 65536 / (std::max(attr.numRegs, 1) * 32));
+    if (const char* knob = std::getenv("LUNA_B200_MAXW")) max_warps = std::max(1, std::min(max_warps, std::atoi(knob)));
+    int max_stages = kMaxRowStages;
+    if (const char* knob = std::getenv("LUNA_B200_ROW_STAGES")) max_stages = std::max(2, std::min(max_stages, std::atoi(knob)));
+    const size_t budget = static_cast<size_t>(dt.max_smem_optin);
+    for (int w = max_warps; w >= 1 && r.depth == 0; --w)
+      for (int st = max_stages; st >= 2 && r.depth == 0; --st)
+        for (int depth = std::min(4, 2 * f.nkinds); depth >= 2; --depth) {
+          const size_t bytes = sparse_shared_bytes<T>(f) + w * (depth * sparse_slot_bytes<T>(f) + sparse_fixed_bytes<T>(f, st));
+          if (bytes > budget) continue;
+          r.depth = depth;
+          r.warps = w;
+          r.ctas = 1;
+          r.block_bytes = bytes;
+          row_stages = st;
+          break;
+        }
+  }
   if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
   P.slots = r.depth;
+  P.row_stages = row_stages;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(r.block_bytes)));
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);

@@ -218,11 +218,13 @@ def test_input_validation_errors():
 
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
 @pytest.mark.parametrize("name", ["cfg2", "cfg5", "cfg4"])
-@pytest.mark.parametrize("knob", ["LUNA_B200_NO_CANON", "LUNA_B200_NO_SPARSE"])
+@pytest.mark.parametrize("knob", ["LUNA_B200_NO_CANON=1", "LUNA_B200_NO_SPARSE=1", "LUNA_B200_BWD_KERNEL=row",
+                                  "LUNA_B200_BWD_KERNEL=units"])
 def test_staged_kernel_variants_match_oracle(name, dtype, knob, monkeypatch):
-    """The canonical configurations through the kernels they do not take by default: loops over run-time path
-    tables (NO_CANON) and the unrolled kernel with dense coupling matrices (NO_SPARSE)."""
-    monkeypatch.setenv(knob, "1")
+    """The canonical configurations through the kernels they do not all take by default: loops over run-time path
+    tables (NO_CANON), the unrolled kernel with dense coupling matrices (NO_SPARSE), and the two data-movement
+    variants of the backward kernel with compiled-in coupling patterns (row stages / unit ring)."""
+    monkeypatch.setenv(*knob.split("="))
     conv = run_case(name, dtype, nodes=37, edges=301, seed=3)
     assert conv.op.uses_staged_kernels and conv.op.canonical_l2 >= 0
 
