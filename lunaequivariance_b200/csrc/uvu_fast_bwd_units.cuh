@@ -244,7 +244,14 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_u
 
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t pe = P.src_rowptr[n + 1];
-    if (pos >= pe) continue;  // no out-edges: the row of gx was zero-filled (or is left as it is) by the launcher
+    if (pos >= pe) {
+      // No out-edges: the row of gx was zero-filled (or is left as it is) by the launcher.  A run of such rows (a
+      // destination-range shard has hundreds of thousands) is jumped over with one search for the row that holds the
+      // warp's next edge, not walked one dependent load at a time.
+      if (pos >= p_end) break;
+      n = warp_lower_bound(P.src_rowptr, N, pos + 1, lane) - 2;
+      continue;
+    }
     {
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
