@@ -70,7 +70,7 @@ def irreps_of(name):
 
 
 def build_paths(name):
-    from lunaequivariance_b200 import workloads
+    import bench_workloads as workloads
 
     in1, in2, out, dtype, atoms, kind, lmax = irreps_of(name)
     instructions = [(0, 0, 0, "uvu", True)] if name == "cfg1" else workloads.all_uvu_instructions(in1, in2, out)
@@ -79,7 +79,7 @@ def build_paths(name):
 
 def build_graph_edges(name, atoms_per_gpu, world, rank, device):
     """This rank's destination-sorted edge slice (global ids) and unit edge vectors."""
-    from lunaequivariance_b200 import workloads
+    import bench_workloads as workloads
 
     kind = WORKLOADS[name][5]
     total = atoms_per_gpu * world

@@ -1,7 +1,7 @@
-"""Synthetic graphs with the shapes of molecular-dynamics workloads: periodic radius graphs and fixed-degree graphs.
+"""Synthetic graphs for the benchmark and the full-size parity tests: periodic radius graphs and fixed-degree graphs.
 
-These generators produce destination-sorted edge lists (what a neighbour list of an MD code looks like) on the
-device of the input, for examples, tests and the benchmark.  Atoms are numbered in cell order (a z-fastest sweep
+Not part of the library: these generators stand in for the neighbour list of an MD code.  They produce
+destination-sorted edge lists on the device of the input.  Atoms are numbered in cell order (a z-fastest sweep
 over the cells of a uniform grid), so consecutive destination nodes share most of their sources - the numbering an
 MD neighbour list gives - and contiguous destination ranges are spatial slabs.
 """
@@ -15,7 +15,7 @@ import torch
 
 def all_uvu_instructions(irreps_in1, irreps_in2, irreps_out):
     """Every parity-allowed (i_in1, i_in2, i_out, 'uvu', True) triple, in (i, j, k) order."""
-    from .irreps import as_irreps
+    from lunaequivariance_b200.irreps import as_irreps
 
     in1, in2, out = as_irreps(irreps_in1), as_irreps(irreps_in2), as_irreps(irreps_out)
     return [(i, j, k, "uvu", True)
@@ -106,16 +106,5 @@ def random_unit_vectors(count: int, seed: int, device, dtype=torch.float64):
     return torch.nn.functional.normalize(v, dim=-1).to(device=device, dtype=dtype)
 
 
-def balanced_node_ranges(dst_rowptr: torch.Tensor, parts: int) -> list[tuple[int, int]]:
-    """Contiguous destination ranges with near-equal edge counts (row-pointer search, not node counts)."""
-    rowptr = dst_rowptr.to("cpu", torch.int64)
-    total, nodes = int(rowptr[-1]), rowptr.numel() - 1
-    cuts = [0]
-    for part in range(1, parts):
-        cuts.append(int(torch.searchsorted(rowptr, torch.tensor(total * part // parts)).clamp(max=nodes)))
-    cuts.append(nodes)
-    return [(cuts[i], max(cuts[i], cuts[i + 1])) for i in range(parts)]
-
-
 __all__ = ["all_uvu_instructions", "periodic_positions", "radius_graph_periodic", "fixed_degree_graph",
-           "random_unit_vectors", "balanced_node_ranges"]
+           "random_unit_vectors"]

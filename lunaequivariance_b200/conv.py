@@ -145,6 +145,17 @@ class LunaTPUVUConv:
         """Whether the backward kernel with compiled-in coupling patterns applies."""
         return self._plan.query(6) > 0
 
+    def check_status(self, device=None) -> None:
+        """Raise ``RuntimeError`` if a kernel of this operator gave up a bounded wait since the last check.
+
+        The staged kernels wait for their bulk copies with an iteration limit; a warp whose wait runs out records a
+        code in the plan's device status word and returns, leaving its outputs partly written.  This call reads the
+        word on the current stream of ``device`` (it synchronises that stream) and clears it.
+        """
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        with torch.cuda.device(device):
+            _native.check(_native.library().luna_uvu_check_status(self._plan.handle, _native.current_stream(device)))
+
     def force_generic(self, enabled: bool = True) -> None:
         """Route every call through the table-driven kernels (for comparisons and tests)."""
         _native.check(_native.library().luna_uvu_plan_set_generic(self._plan.handle, int(enabled)))
@@ -209,10 +220,15 @@ def _prepared(tensor: torch.Tensor | None) -> torch.Tensor | None:
     return tensor
 
 
-def _check_inputs(op: LunaTPUVUConv, x, y, w, source_rows, num_edges) -> None:
+def _check_inputs(op: LunaTPUVUConv, x, y, w, source_rows, num_edges, *, g=None, num_nodes=0, rx=None, ry=None,
+                  rw=None) -> None:
     _require_cuda(x)
     for name, t, rows, cols in (("x", x, source_rows, op.in1_dim), ("edge_attr", y, num_edges, op.in2_dim),
-                                ("weight", w, num_edges, op.weight_numel)):
+                                ("weight", w, num_edges, op.weight_numel), ("grad_out", g, num_nodes, op.out_dim),
+                                ("rx", rx, source_rows, op.in1_dim), ("ry", ry, num_edges, op.in2_dim),
+                                ("rw", rw, num_edges, op.weight_numel)):
+        if t is None:
+            continue
         if t.dtype != op.compute_dtype:
             raise TypeError(f"{name} must be {op.compute_dtype}, got {t.dtype}")
         if t.device != x.device:
@@ -265,8 +281,10 @@ def run_forward(op: LunaTPUVUConv, x, y, w, graph) -> torch.Tensor:
 
 def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True)):
     struct, n, ns, e = _graph_struct(graph)
-    _check_inputs(op, x, y, w, ns, e)
+    _check_inputs(op, x, y, w, ns, e, g=g, num_nodes=n)
     x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
+    if not any(needs):
+        return None, None, None
     gx = torch.empty_like(x) if needs[0] else None
     gy = torch.empty_like(y) if needs[1] else None
     gw = torch.empty_like(w) if needs[2] else None
@@ -283,9 +301,11 @@ def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True))
 
 def run_double_backward(op: LunaTPUVUConv, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True)):
     struct, n, ns, e = _graph_struct(graph)
-    _check_inputs(op, x, y, w, ns, e)
+    _check_inputs(op, x, y, w, ns, e, g=g, num_nodes=n, rx=rx, ry=ry, rw=rw)
     x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
     rx, ry, rw = _prepared(rx), _prepared(ry), _prepared(rw)
+    if not any(needs):
+        return None, None, None, None
     hx = torch.empty_like(x) if needs[0] else None
     hy = torch.empty_like(y) if needs[1] else None
     hw = torch.empty_like(w) if needs[2] else None
@@ -305,6 +325,42 @@ def run_double_backward(op: LunaTPUVUConv, x, y, w, g, rx, ry, rw, graph, needs=
 # ----------------------------------------------------------------------------------------------- eager autograd chain
 
 
+def _engine_needs(needs) -> tuple:
+    """Which gradients of the running autograd node's tensor inputs (``needs`` lists them in order) will be used.
+
+    ``ctx.needs_input_grad`` only says which inputs require grad.  Under ``torch.autograd.grad(outputs, inputs)`` the
+    engine also knows which of them lie on a path to the requested ``inputs``: a gradient whose consumer node will not
+    run is dropped right after this node returns it.  The force-training step is the case that matters: the energy is
+    differentiated with respect to the edge vectors only, yet the per-edge weights require grad for the later loss, so
+    without this a weight-sized gradient would be computed and thrown away.  Any doubt (no engine information, a
+    consumer the engine cannot be asked about, an API change) counts as "used".
+    """
+    needs = tuple(bool(n) for n in needs)
+    try:
+        consumers = torch._C._current_autograd_node().next_functions
+        if len(consumers) != len(needs):  # one edge per tensor input; anything else is not understood
+            return needs
+    except Exception:
+        return needs
+    narrowed = []
+    for need, (consumer, _) in zip(needs, consumers):
+        if need and consumer is not None:
+            try:
+                need = bool(torch._C._will_engine_execute_node(consumer))
+            except Exception:  # e.g. a leaf's accumulator cannot be queried under autograd.grad
+                need = True
+        narrowed.append(need and consumer is not None)
+    return tuple(narrowed)
+
+
+def _through_view(tensor):
+    """A leaf that requires grad, seen through a no-copy view: the view's autograd node, unlike the leaf's own
+    accumulator, can be asked whether the running backward pass will reach it (see ``_engine_needs``)."""
+    if tensor is not None and tensor.requires_grad and tensor.is_leaf and torch.is_grad_enabled():
+        return tensor.view_as(tensor)
+    return tensor
+
+
 class UVUConvForward(torch.autograd.Function):
     @staticmethod
     def forward(ctx, op, x, y, w, graph):
@@ -320,46 +376,49 @@ class UVUConvForward(torch.autograd.Function):
         needs = ctx.needs_input_grad[1:4]
         if grad_out is None:
             return (None,) + tuple(torch.zeros_like(t) if need else None for t, need in zip((x, y, w), needs)) + (None,)
+        needs = _engine_needs(needs)
         g = grad_out.contiguous()
         if torch.is_grad_enabled():
-            gx, gy, gw = UVUConvBackward.apply(op, x, y, w, g, graph)
+            gx, gy, gw = UVUConvBackward.apply(op, x, y, w, g, graph, needs)
         else:
             gx, gy, gw = run_backward(op, x, y, w, g, graph, needs=needs)
-        return (None, gx if needs[0] else None, gy if needs[1] else None, gw if needs[2] else None, None)
+        return (None, gx, gy, gw, None)
 
 
 class UVUConvBackward(torch.autograd.Function):
+    """First-order gradients as a differentiable function of (x, y, w, g); ``needs`` selects the outputs."""
+
     @staticmethod
-    def forward(ctx, op, x, y, w, g, graph):
+    def forward(ctx, op, x, y, w, g, graph, needs=(True, True, True)):
         ctx.op, ctx.graph = op, graph
         ctx.set_materialize_grads(False)
         ctx.save_for_backward(x, y, w, g)
-        return run_backward(op, x, y, w, g, graph, needs=(True, True, True))
+        return run_backward(op, x, y, w, g, graph, needs=tuple(needs))
 
     @staticmethod
     def backward(ctx, rx, ry, rw):
         x, y, w, g = ctx.saved_tensors
         needs = ctx.needs_input_grad[1:5]
         if rx is None and ry is None and rw is None:
-            return (None,) * 6
+            return (None,) * 7
+        needs = _engine_needs(needs)
         if torch.is_grad_enabled():
-            hx, hy, hw, hg = UVUConvDoubleBackward.apply(ctx.op, x, y, w, g, rx, ry, rw, ctx.graph)
+            hx, hy, hw, hg = UVUConvDoubleBackward.apply(ctx.op, x, y, w, g, rx, ry, rw, ctx.graph, needs)
         else:
             hx, hy, hw, hg = run_double_backward(ctx.op, x, y, w, g, rx, ry, rw, ctx.graph, needs=needs)
-        return (None, hx if needs[0] else None, hy if needs[1] else None, hw if needs[2] else None,
-                hg if needs[3] else None, None)
+        return (None, hx, hy, hw, hg, None, None)
 
 
 class UVUConvDoubleBackward(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, op, x, y, w, g, rx, ry, rw, graph):
+    def forward(ctx, op, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True)):
         ctx.set_materialize_grads(False)
-        return run_double_backward(op, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True))
+        return run_double_backward(op, x, y, w, g, rx, ry, rw, graph, needs=tuple(needs))
 
     @staticmethod
     def backward(ctx, *grads):
         if all(g is None for g in grads):
-            return (None,) * 9
+            return (None,) * 10
         raise NotImplementedError("third-order derivatives of the UVU convolution are not provided")
 
 
@@ -478,7 +537,7 @@ def lunatp_uvu_conv_func(op: LunaTPUVUConv, x, edge_attr, weight, *, graph: Luna
             x.contiguous(), edge_attr.contiguous(), weight.contiguous(), None, graph.table_list(),
             graph.num_nodes, False, op.torch_config)
         return out
-    return UVUConvForward.apply(op, x, edge_attr, weight, graph)
+    return UVUConvForward.apply(op, _through_view(x), _through_view(edge_attr), _through_view(weight), graph)
 
 
 __all__ = ["LunaTPUVUConv", "create_uvu_conv_operator", "lunatp_uvu_conv_func", "run_forward", "run_backward",

@@ -11,7 +11,7 @@ from collections.abc import Mapping
 import torch
 
 from .conv import create_uvu_conv_operator
-from .functional import tensor_product_conv
+from .functional import require_uvu, resolve_source, tensor_product_conv
 from .graph import make_graph
 from .paths import TensorProductConfig
 from .spherical_harmonics import UNSET, SphericalHarmonicsConfig, parse_irreps, spherical_harmonics
@@ -29,49 +29,40 @@ class TensorProductConv(torch.nn.Module):
                  out_var=None, irrep_normalization=None, path_normalization=None, internal_weights=None,
                  shared_weights=None, *, dtype=None, mode=None):
         super().__init__()
-        metadata = isinstance(irreps_in1, Mapping)
-        if metadata or isinstance(irreps_in1, torch.nn.Module):
-            if any(v is not None for v in (irreps_in2, irreps_out, instructions, in1_var, in2_var, out_var,
-                                           irrep_normalization, path_normalization, internal_weights,
-                                           shared_weights)):
-                raise TypeError("Pass either an existing tensor product/metadata or irreps and path options")
-            tp = irreps_in1
-        else:
-            if irreps_in2 is None or irreps_out is None or instructions is None:
+        options = dict(in1_var=in1_var, in2_var=in2_var, out_var=out_var, irrep_normalization=irrep_normalization,
+                       path_normalization=path_normalization, internal_weights=internal_weights,
+                       shared_weights=shared_weights)
+        prebuilt = isinstance(irreps_in1, (Mapping, torch.nn.Module))
+        if prebuilt and not all(v is None for v in (irreps_in2, irreps_out, instructions, *options.values())):
+            raise TypeError("Pass either an existing tensor product/metadata or irreps and path options")
+
+        def build():
+            if None in (irreps_in2, irreps_out, instructions):
                 raise TypeError("irreps_in2, irreps_out and instructions are required")
-            tp = TensorProductConfig(
-                irreps_in1, irreps_in2, irreps_out, instructions, in1_var=in1_var, in2_var=in2_var,
-                out_var=out_var, irrep_normalization=irrep_normalization, path_normalization=path_normalization,
-                internal_weights=internal_weights, shared_weights=shared_weights)
-            if dtype is not None and tp.weight.dtype != dtype:
-                tp.to(dtype=dtype)
-        if metadata:
-            if mode not in ("uuu", "uvu"):
-                raise ValueError('Prebuilt metadata requires mode="uuu" or mode="uvu"')
-            dtype = torch.float32 if dtype is None else dtype
-        else:
-            modes = {instruction.connection_mode for instruction in tp.instructions}
-            if len(modes) != 1 or not modes <= {"uuu", "uvu", "uvw"}:
-                raise ValueError("TensorProductConv requires one connection mode: uuu, uvu or uvw")
-            inferred = modes.pop()
-            if mode is not None and mode != inferred:
-                raise ValueError("mode must match the tensor-product instructions")
-            mode = inferred
-            dtype = tp.weight.dtype if dtype is None else dtype
-        if mode != "uvu":
-            raise NotImplementedError(f"this build provides the uvu convolution only, got mode {mode!r}")
+            product = TensorProductConfig(irreps_in1, irreps_in2, irreps_out, instructions, **options)
+            if dtype is not None and product.weight.dtype != dtype:
+                product.to(dtype=dtype)
+            return product
+
+        resolved = resolve_source(
+            irreps_in1, build=build, mode=mode,
+            metadata_message='Prebuilt metadata requires mode="uuu" or mode="uvu"',
+            mode_message="TensorProductConv requires one connection mode: uuu, uvu or uvw")
+        require_uvu(resolved.mode, "mode")
+        source = resolved.source
+        if dtype is None:
+            dtype = torch.float32 if resolved.from_metadata else source.weight.dtype
         self.mode = "uvu_conv"
-        self.op = create_uvu_conv_operator(tp, dtype=dtype)
-        if metadata:
-            self.weight_numel = tp["weight_numel"]
+        self.op = create_uvu_conv_operator(source, dtype=dtype)
+        if resolved.from_metadata:
+            self.weight_numel = source["weight_numel"]
             self.internal_weights = self.shared_weights = False
-        else:
-            self.tp = tp
-            self.irreps_in1, self.irreps_in2, self.irreps_out = tp.irreps_in1, tp.irreps_in2, tp.irreps_out
-            self.instructions = tp.instructions
-            self.weight_numel = tp.weight_numel
-            self.internal_weights, self.shared_weights = tp.internal_weights, tp.shared_weights
-            self.train(getattr(tp, "training", True))
+            return
+        self.tp = source
+        for name in ("irreps_in1", "irreps_in2", "irreps_out", "instructions", "weight_numel", "internal_weights",
+                     "shared_weights"):
+            setattr(self, name, getattr(source, name))
+        self.train(getattr(source, "training", True))
 
     @property
     def weight(self):
@@ -99,45 +90,59 @@ class TensorProductConv(torch.nn.Module):
         return tensor_product_conv(x, edge_attr, weight, graph=graph, config=self.op, **kwargs)
 
 
+_SH_DTYPES = (torch.float16, torch.bfloat16, torch.float32, torch.float64)
+
+
+def _checked_sh_dtype(dtype):
+    if dtype not in _SH_DTYPES:
+        raise ValueError("SphericalHarmonics requires a floating dtype")
+    return dtype
+
+
 class SphericalHarmonics(torch.nn.Module):
-    """Real spherical harmonics of a 3-vector, e3nn conventions, degrees through 12."""
+    """Real spherical harmonics of a 3-vector, e3nn conventions, degrees through 12.
+
+    The module is a thin holder of one ``SphericalHarmonicsConfig``; ``irreps_in``, ``irreps_out``, ``normalize``
+    and ``normalization`` read through to it.  ``.to()/.double()/.float()`` move a zero-element anchor tensor, which is
+    how the module learns its new dtype.
+    """
 
     def __init__(self, irreps_out, normalize=UNSET, normalization="integral", irreps_in=None, *, dtype=None):
         super().__init__()
-        if hasattr(irreps_out, "_ls_list"):
-            other = irreps_out
-            self.training = other.training
-            irreps_out, normalize, normalization, irreps_in = (
-                tuple(other._ls_list), other.normalize, other.normalization, other.irreps_in)
+        if hasattr(irreps_out, "_ls_list"):  # another harmonics module (this library's, the reference's, e3nn's)
+            template, irreps_out = irreps_out, tuple(irreps_out._ls_list)
+            normalize, normalization, irreps_in = template.normalize, template.normalization, template.irreps_in
+            self.training = template.training
         if normalize is UNSET:
             raise TypeError("SphericalHarmonics requires normalize=True or False")
         if normalization not in ("component", "norm", "integral"):
             raise ValueError("normalization must be component, norm or integral")
-        if dtype is None:
-            dtype = torch.get_default_dtype()
-        if dtype not in (torch.float16, torch.bfloat16, torch.float32, torch.float64):
-            raise ValueError("SphericalHarmonics requires a floating dtype")
-        self.irreps_in, self.irreps_out, degrees = parse_irreps(irreps_out, irreps_in)
-        self._ls_list = list(degrees)
-        self._lmax = max(degrees)
-        self.normalize, self.normalization = bool(normalize), normalization
-        self.compute_dtype = dtype
-        self._dtype_anchor = torch.empty(0, dtype=dtype)
+        self._dtype_anchor = torch.empty(0, dtype=_checked_sh_dtype(torch.get_default_dtype() if dtype is None else dtype))
+        self._config = SphericalHarmonicsConfig(irreps_out, normalize, normalization, self._dtype_anchor.dtype,
+                                                irreps_in=irreps_in)
         self.last_execution_backend = "uninitialized"
 
+    irreps_in = property(lambda self: self._config.irreps_in)
+    irreps_out = property(lambda self: self._config.irreps_out)
+    normalize = property(lambda self: self._config.normalize)
+    normalization = property(lambda self: self._config.normalization)
+    compute_dtype = property(lambda self: self._dtype_anchor.dtype)
+    _ls_list = property(lambda self: list(self._config._ls_list))
+    _lmax = property(lambda self: self._config._lmax)
+
     def _apply(self, fn, recurse=True):
-        anchor = fn(self._dtype_anchor)
-        if anchor.dtype not in (torch.float16, torch.bfloat16, torch.float32, torch.float64):
-            raise ValueError("SphericalHarmonics requires a floating dtype")
+        moved = fn(self._dtype_anchor)
+        _checked_sh_dtype(moved.dtype)
         result = super()._apply(fn, recurse=recurse)
-        self._dtype_anchor = anchor
-        self.compute_dtype = anchor.dtype
+        self._dtype_anchor = moved
         return result
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        config = SphericalHarmonicsConfig(tuple(self._ls_list), self.normalize, self.normalization, x.dtype,
-                                          irreps_in=str(self.irreps_in))
-        result = spherical_harmonics(self._ls_list, x, self.normalize, self.normalization, config=config)
+        config = self._config
+        if config.compute_dtype != x.dtype:  # evaluate in the dtype of the input, as the functional form does
+            config = SphericalHarmonicsConfig(config._ls_list, config.normalize, config.normalization, x.dtype,
+                                              irreps_in=str(config.irreps_in))
+        result = spherical_harmonics(config._ls_list, x, config.normalize, config.normalization, config=config)
         self.last_execution_backend = "cuda_fused"
         return result
 

@@ -188,76 +188,73 @@ class TensorProductConfig(torch.nn.Module):
             self.register_buffer("weight", torch.Tensor())
 
 
+def _narrowed_terms(l1: int, l2: int, l3: int, path_weight: float, dtype: torch.dtype):
+    """Sparse coupling terms ``(i, j, k, value)`` of one instruction in the coefficient dtype."""
+    terms = cg_terms(l1, l2, l3, path_weight)
+    if dtype != torch.float32:
+        return terms
+    # The reference rounds the coupling tensor to float32 before it multiplies by the path weight
+    # (src/lunatp/utils/cg.py:31-41 on a float32 tensor); doing the same keeps the coefficients bit-identical.
+    import numpy as np
+
+    from .coupling import wigner_3j
+
+    rounded = wigner_3j(l1, l2, l3).astype(np.float32)
+    return [(i, j, k, float(rounded[i, j, k]) * path_weight) for i, j, k, _ in terms]
+
+
 def build_uvu_conv_metadata(tp, coefficient_dtype: torch.dtype = torch.float64) -> dict:
-    """Lower UVU instructions to flat per-path specs (offsets, dims, sparse coupling terms)."""
+    """Lower UVU instructions to flat per-path specs (offsets, dims, sparse coupling terms).
+
+    The returned dict has the reference's format (``src/lunatp/uvu_conv/kernels/utils.py:23-119``) so that either
+    library's metadata can be handed to the other's operator: one spec per (instruction, channel ``v`` of the second
+    input); element ``u`` of that spec's weights sits at ``weight_offset + u * weight_stride``.
+    """
     if coefficient_dtype not in (torch.float32, torch.float64):
         raise ValueError(f"UVU convolution coefficients require float32 or float64; got {coefficient_dtype}.")
-    if tp.internal_weights:
-        raise ValueError("Generated SO3 kernels require internal_weights=False.")
-    if tp.shared_weights:
-        raise ValueError("Generated SO3 kernels require shared_weights=False.")
-    in1, in2, out = as_irreps(tp.irreps_in1), as_irreps(tp.irreps_in2), as_irreps(tp.irreps_out)
-    start1 = [s.start for s in in1.slices()]
-    start2 = [s.start for s in in2.slices()]
-    start_out = [s.start for s in out.slices()]
+    for flag in ("internal_weights", "shared_weights"):
+        if getattr(tp, flag):
+            raise ValueError(f"Generated SO3 kernels require {flag}=False.")
+    blocks = [as_irreps(r) for r in (tp.irreps_in1, tp.irreps_in2, tp.irreps_out)]
+    starts = [[piece.start for piece in irreps.slices()] for irreps in blocks]
 
     specs: list[dict] = []
-    weight_cursor = 0
-    max_channels = 0
-    for index, ins in enumerate(tp.instructions):
+    widest = 0
+    weights_used = 0
+    for position, ins in enumerate(tp.instructions):
         if ins.connection_mode != "uvu":
             raise ValueError(f"Only connection_mode='uvu' is supported, got {ins.connection_mode!r}.")
         if not ins.has_weight:
             raise ValueError("Generated SO3 kernels require weighted uvu instructions.")
-        (mul1, ir1), (mul2, ir2), (mul_out, ir_out) = in1[ins.i_in1], in2[ins.i_in2], out[ins.i_out]
-        if mul1 != mul_out:
+        slots = (ins.i_in1, ins.i_in2, ins.i_out)
+        (mul1, ir1), (mul2, ir2), (mul3, ir3) = (irreps[slot] for irreps, slot in zip(blocks, slots))
+        if mul1 != mul3:
             raise ValueError(
-                f"UVU requires equal input/output multiplicities; got {mul1} and {mul_out} "
+                f"UVU requires equal input/output multiplicities; got {mul1} and {mul3} "
                 f"for path ({ins.i_in1}, {ins.i_in2}, {ins.i_out})."
             )
         if tuple(ins.path_shape) != (mul1, mul2):
             raise ValueError(f"UVU expects path_shape=({mul1}, {mul2}); got {tuple(ins.path_shape)}.")
-        max_channels = max(max_channels, mul1)
-        terms = cg_terms(ir1.l, ir2.l, ir_out.l, float(ins.path_weight))
-        if coefficient_dtype == torch.float32:
-            # The reference narrows the coupling tensor before scaling (cg.py:31-41 with a float32 tensor).
-            import numpy as np
-
-            from .coupling import wigner_3j
-
-            narrow = wigner_3j(ir1.l, ir2.l, ir_out.l).astype(np.float32)
-            terms = [(i, j, k, float(narrow[i, j, k]) * float(ins.path_weight)) for i, j, k, _ in terms]
-        for v in range(mul2):
-            spec = {
-                "x_offset": start1[ins.i_in1],
-                "y_offset": start2[ins.i_in2] + v * ir2.dim,
-                "out_offset": start_out[ins.i_out],
-                "weight_offset": weight_cursor + v,
-                "channels": mul1,
-                "d1": ir1.dim, "d2": ir2.dim, "d3": ir_out.dim,
-                "l1": ir1.l, "l2": ir2.l, "l3": ir_out.l,
-                "terms": terms,
-            }
-            if mul2 != 1:
-                spec["weight_stride"] = mul2
-                spec["l0_path"] = index
-            specs.append(spec)
-        weight_cursor += mul1 * mul2
+        x_start, y_start, out_start = (table[slot] for table, slot in zip(starts, slots))
+        shared = dict(x_offset=x_start, out_offset=out_start, channels=mul1, d1=ir1.dim, d2=ir2.dim, d3=ir3.dim,
+                      l1=ir1.l, l2=ir2.l, l3=ir3.l,
+                      terms=_narrowed_terms(ir1.l, ir2.l, ir3.l, float(ins.path_weight), coefficient_dtype))
+        # several channels of the second input share the instruction's weight block, interleaved [u, v]
+        extra = dict(weight_stride=mul2, l0_path=position) if mul2 != 1 else {}
+        specs += [dict(shared, y_offset=y_start + v * ir2.dim, weight_offset=weights_used + v, **extra)
+                  for v in range(mul2)]
+        weights_used += mul1 * mul2
+        widest = max(widest, mul1)
 
     if not specs:
         raise ValueError("No uvu instructions found.")
-    if weight_cursor != tp.weight_numel:
-        raise ValueError(f"Lowered weight_numel={weight_cursor}, but configuration reports {tp.weight_numel}.")
-    if any(spec["channels"] <= 0 for spec in specs):
+    if weights_used != tp.weight_numel:
+        raise ValueError(f"Lowered weight_numel={weights_used}, but configuration reports {tp.weight_numel}.")
+    if min(spec["channels"] for spec in specs) <= 0:
         raise ValueError("SO3 uvu kernels require positive channels per irrep.")
-    return {
-        "in1_dim": in1.dim,
-        "in2_dim": in2.dim,
-        "out_dim": out.dim,
-        "weight_numel": int(tp.weight_numel),
-        "max_channels": max_channels,
-        "generated_specs": specs,
-    }
+    in1, in2, out = blocks
+    return dict(in1_dim=in1.dim, in2_dim=in2.dim, out_dim=out.dim, weight_numel=int(tp.weight_numel),
+                max_channels=widest, generated_specs=specs)
 
 
 __all__ = ["Instruction", "TensorProductPaths", "TensorProductConfig", "build_uvu_conv_metadata", "Irreps"]

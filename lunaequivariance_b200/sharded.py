@@ -67,6 +67,17 @@ def make_graph_shard(src_global: torch.Tensor, dst_global: torch.Tensor, node_co
     return GraphShard(graph=graph, node_begin=begin, node_counts=node_counts, padded_rows=padded, group=group)
 
 
+def balanced_node_ranges(dst_rowptr: torch.Tensor, parts: int) -> list[tuple[int, int]]:
+    """Contiguous destination ranges with near-equal edge counts (row-pointer search, not node counts)."""
+    rowptr = dst_rowptr.to("cpu", torch.int64)
+    total, nodes = int(rowptr[-1]), rowptr.numel() - 1
+    cuts = [0]
+    for part in range(1, parts):
+        cuts.append(int(torch.searchsorted(rowptr, torch.tensor(total * part // parts)).clamp(max=nodes)))
+    cuts.append(nodes)
+    return [(cuts[i], max(cuts[i], cuts[i + 1])) for i in range(parts)]
+
+
 def _all_gather_rows(x_padded: torch.Tensor, world: int, group) -> torch.Tensor:
     out = x_padded.new_empty((world * x_padded.shape[0], *x_padded.shape[1:]))
     dist.all_gather_into_tensor(out, x_padded.contiguous(), group=group)
@@ -131,4 +142,5 @@ def sharded_conv(conv, x_local: torch.Tensor, edge_attr: torch.Tensor, weight: t
     return conv(gather_sources(x_local, shard), edge_attr, weight, graph=shard.graph)
 
 
-__all__ = ["GraphShard", "make_graph_shard", "gather_sources", "sharded_conv", "padded_source_index"]
+__all__ = ["GraphShard", "make_graph_shard", "gather_sources", "sharded_conv", "padded_source_index",
+           "balanced_node_ranges"]

@@ -12,7 +12,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from lunaequivariance_b200 import sharded, workloads
+import bench_workloads as workloads
+from lunaequivariance_b200 import sharded
 from oracle import uvu_conv as oracle_conv
 
 
@@ -81,7 +82,7 @@ def test_padded_source_index_and_ranges():
     index = sharded.padded_source_index(torch.tensor([0, 2, 3, 7, 8, 9]), counts, 5)
     assert index.tolist() == [0, 2, 5, 9, 10, 11]
     rowptr = torch.tensor([0, 10, 10, 30, 35, 60, 100])
-    ranges = workloads.balanced_node_ranges(rowptr, 2)
+    ranges = sharded.balanced_node_ranges(rowptr, 2)
     assert ranges[0][0] == 0 and ranges[-1][1] == 6 and ranges[0][1] == ranges[1][0]
     with pytest.raises(ValueError, match="range"):
         sharded.make_graph_shard(torch.tensor([0]), torch.tensor([4]), (3, 3), 0)
