@@ -13,6 +13,19 @@ import math
 import torch
 
 
+WORKLOADS = {
+    # name: (irreps_in1, sh lmax, irreps_out, dtype, atoms per GPU, graph kind)
+    "cfg2": ("128x0e+128x1o+128x2e", 3, "128x0e+128x1o+128x2e+128x3o", torch.float32, 50_000, "radius"),
+    # cfg3 is cfg2's convolution in FP64 inside a force-training step (energy -> forces -> loss -> dL/dweight)
+    "cfg3": ("128x0e+128x1o+128x2e", 3, "128x0e+128x1o+128x2e+128x3o", torch.float64, 20_000, "radius"),
+    "cfg5": ("64x0e+64x1o+64x2e", 2, "64x0e+64x1o+64x2e", torch.float32, 250_000, "radius"),
+    "cfg4": ("64x0e+64x1o+64x2e+64x3o", 3, "64x0e+64x1o+64x2e+64x3o", torch.float32, 100_000, "degree40"),
+    "cfg1": ("32x1o", 1, "32x0e", torch.float64, 1_000, "degree16"),
+    "lmax1": ("128x0e+128x1o", 1, "128x0e+128x1o", torch.float32, 100_000, "radius"),
+}
+DENSITY, CUTOFF = 0.1, 5.0
+
+
 def all_uvu_instructions(irreps_in1, irreps_in2, irreps_out):
     """Every parity-allowed (i_in1, i_in2, i_out, 'uvu', True) triple, in (i, j, k) order."""
     from lunaequivariance_b200.irreps import as_irreps
@@ -105,6 +118,37 @@ def random_unit_vectors(count: int, seed: int, device, dtype=torch.float64):
     v = torch.randn(count, 3, generator=generator, dtype=torch.float64)
     return torch.nn.functional.normalize(v, dim=-1).to(device=device, dtype=dtype)
 
+def irreps_of(name):
+    in1, lmax, out, dtype, atoms, kind = WORKLOADS[name]
+    in2 = "+".join(f"1x{l}{'e' if l % 2 == 0 else 'o'}" for l in range(lmax + 1))
+    if name == "cfg1":
+        in2 = "1x1o"
+    return in1, in2, out, dtype, atoms, kind, lmax
 
-__all__ = ["all_uvu_instructions", "periodic_positions", "radius_graph_periodic", "fixed_degree_graph",
+
+def build_paths(name):
+    in1, in2, out, dtype, atoms, kind, lmax = irreps_of(name)
+    instructions = [(0, 0, 0, "uvu", True)] if name == "cfg1" else all_uvu_instructions(in1, in2, out)
+    return in1, in2, out, instructions, dtype, atoms, kind, lmax
+
+
+def build_graph_edges(name, atoms_per_gpu, world, rank, device):
+    """This rank's destination-sorted edge slice (global ids) and unit edge vectors."""
+    kind = WORKLOADS[name][5]
+    total = atoms_per_gpu * world
+    begin, end = rank * atoms_per_gpu, (rank + 1) * atoms_per_gpu
+    if kind == "radius":
+        pos, box, cells = periodic_positions(total, DENSITY, 0, device, CUTOFF)
+        src, dst, vec = radius_graph_periodic(pos, box, CUTOFF, cells, begin, end)
+        return src, dst, vec
+    degree = 40 if kind == "degree40" else 16
+    src, dst = fixed_degree_graph(total, degree, 0, device)
+    mine = (dst >= begin) & (dst < end)
+    src, dst = src[mine], dst[mine]
+    vec = random_unit_vectors(src.numel(), 1 + rank, device)
+    return src, dst, vec
+
+
+__all__ = ["WORKLOADS", "DENSITY", "CUTOFF", "irreps_of", "build_paths", "build_graph_edges",
+           "all_uvu_instructions", "periodic_positions", "radius_graph_periodic", "fixed_degree_graph",
            "random_unit_vectors"]

@@ -91,9 +91,17 @@ typedef enum {
   LUNA_PLAN_BWD_SMEM_BYTES = 4,
   LUNA_PLAN_CANONICAL_L2 = 5,   /* highest edge-attribute degree if the path list is the full list of allowed
                                    (l1, l2, l3) couplings in standard order (kernels unrolled at compile time), else -1 */
-  LUNA_PLAN_SPARSE_TERMS = 6    /* > 0 if the plan's coupling terms have the compiled-in non-zero patterns, so the
+  LUNA_PLAN_SPARSE_TERMS = 6,   /* > 0 if the plan's coupling terms have the compiled-in non-zero patterns, so the
                                    backward kernel with per-lane contraction of the edge-attribute gradient applies */
+  LUNA_PLAN_BWD_VARIANT = 7     /* which first-order backward kernel aligned inputs get: a luna_bwd_variant */
 } luna_plan_query;
+typedef enum {
+  LUNA_BWD_TABLE_DRIVEN = 0, /* one thread per output element, any configuration */
+  LUNA_BWD_STAGED_TABLES = 1, /* staged kernel that reads the path list from tables */
+  LUNA_BWD_ROW_STAGES = 2,    /* compiled-in coupling patterns, one warp per edge, whole weight rows staged */
+  LUNA_BWD_UNIT_RING = 3,     /* compiled-in coupling patterns, one warp per edge, (edge, degree) units in a ring */
+  LUNA_BWD_WARP_TEAMS = 4     /* compiled-in coupling patterns, several warps share an edge's staged rows */
+} luna_bwd_variant;
 LUNA_API int64_t luna_uvu_plan_query(const luna_uvu_plan* plan, int what);
 
 /* Force the table-driven kernels (1) or let the plan choose (0, default).  For tests and comparisons. */
@@ -134,18 +142,21 @@ LUNA_API int luna_uvu_conv_bwd(luna_uvu_plan* plan, const luna_graph* graph, con
  * not hit cudaMalloc's device-wide synchronisation, processes whose memory pool is fixed at start-up.  No
  * counterpart in the reference (its operators allocate through torch).  The partial rows that luna_uvu_conv_bwd
  * keeps in caller scratch live in an array built into the library instead:
- *   - the array is luna_uvu_conv_noalloc_max_scratch_bytes() = 8 MiB and occupies that much memory on every GPU
- *     that loads the library, until the process exits;
- *   - a graph for which luna_uvu_conv_scratch_bytes exceeds it is refused with LUNA_ERR_SCRATCH;
- *   - the call itself performs no cudaMalloc/cudaFree.  The plan's tables must therefore already be on the
- *     current device (any earlier call with the plan there, e.g. luna_uvu_check_status, uploads them); if they
- *     are not, LUNA_ERR_INVALID_ARGUMENT is returned instead of allocating;
- *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first
- *     call before starting any stream capture;
+ *   - the array is luna_uvu_conv_noalloc_max_scratch_bytes() = 8 MiB.  It occupies that much memory on a GPU from
+ *     the moment this part of the library is loaded there (with the runtime's default lazy loading: the set-up
+ *     call below; with eager loading: context creation) until the process exits;
+ *   - set-up, once per plan and device, with that device current, before any stream capture and outside the part
+ *     of the program that must not allocate: luna_uvu_conv_noalloc_prepare(plan).  It looks up the array's device
+ *     address (cudaGetSymbolAddress) and uploads the plan's lookup tables (one cudaMalloc);
+ *   - luna_uvu_conv_bwd_noalloc itself performs no cudaMalloc/cudaFree and loads nothing: on a plan or device that
+ *     has not been prepared it returns LUNA_ERR_INVALID_ARGUMENT instead;
+ *   - a call that wants gy on a graph for which luna_uvu_conv_scratch_bytes exceeds the array is refused with
+ *     LUNA_ERR_SCRATCH (without gy no scratch is used and any size is accepted);
  *   - every call on a device uses the same array, which still holds the previous call's partial rows (the kernel
  *     overwrites all rows it reads, nothing needs clearing).  Calls that overlap on one GPU race on it: issue them
  *     in stream order. */
 LUNA_API int64_t luna_uvu_conv_noalloc_max_scratch_bytes(void);
+LUNA_API int luna_uvu_conv_noalloc_prepare(luna_uvu_plan* plan);
 LUNA_API int luna_uvu_conv_bwd_noalloc(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,
                               const void* w, const void* g, void* gx, void* gy, void* gw, void* stream);
 
@@ -200,6 +211,13 @@ LUNA_API int luna_sh_bwd(const luna_sh_desc* desc, const void* v, const void* g,
 /* With rx[n,3] the cotangent of dx: sx[n,3] = d<rx,dx>/dv, sg[n,C] = d<rx,dx>/dg = J rx; null outputs skipped. */
 LUNA_API int luna_sh_dbl_bwd(const luna_sh_desc* desc, const void* v, const void* g, const void* rx, void* sx, void* sg,
                     int64_t n, void* stream);
+
+/* --------------------------------------------------------------------------------------------------------------
+ * Measurement aid, no counterpart in the reference: launches register-resident chains of fused multiply-adds
+ * (kind 0: packed FP32 pairs, the instruction the FP32 kernels run on; kind 1: FP64) and returns the FLOPs the
+ * launch performs in *flops.  Timed by the caller with events on `stream`, it gives the GPU's measured arithmetic
+ * peak, the denominator of the arithmetic roofline.  sink: device buffer of at least 1025 doubles. */
+LUNA_API int luna_probe_fma(int kind, int iterations, void* sink, double* flops, void* stream);
 
 #ifdef __cplusplus
 }

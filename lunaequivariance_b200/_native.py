@@ -90,6 +90,7 @@ _SIGNATURES = {
     "luna_uvu_conv_bwd": (ctypes.c_int, [_P, ctypes.POINTER(Graph), _P, _P, _P, _P, _P, _P, _P, _P,
                                          ctypes.c_int64, _P]),
     "luna_uvu_conv_noalloc_max_scratch_bytes": (ctypes.c_int64, []),
+    "luna_uvu_conv_noalloc_prepare": (ctypes.c_int, [_P]),
     "luna_uvu_conv_bwd_noalloc": (ctypes.c_int, [_P, ctypes.POINTER(Graph), _P, _P, _P, _P, _P, _P, _P, _P]),
     "luna_uvu_conv_dbl_bwd": (ctypes.c_int, [_P, ctypes.POINTER(Graph), _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                              _P, _P, ctypes.c_int64, _P]),
@@ -100,6 +101,7 @@ _SIGNATURES = {
                                          ctypes.POINTER(ctypes.c_int), _P, ctypes.c_int64, _P]),
     "luna_graph_build": (ctypes.c_int, [_P, _P, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                         ctypes.POINTER(GraphOut), _P, ctypes.c_int64, _P]),
+    "luna_probe_fma": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _P, ctypes.POINTER(ctypes.c_double), _P]),
     "luna_sh_fwd": (ctypes.c_int, [ctypes.POINTER(ShDesc), _P, _P, ctypes.c_int64, _P]),
     "luna_sh_bwd": (ctypes.c_int, [ctypes.POINTER(ShDesc), _P, _P, _P, ctypes.c_int64, _P]),
     "luna_sh_dbl_bwd": (ctypes.c_int, [ctypes.POINTER(ShDesc), _P, _P, _P, _P, _P, ctypes.c_int64, _P]),

@@ -114,6 +114,7 @@ class LunaTPUVUConv:
         self.lunatp_dtype = dtype
         self._plan = _Plan(self.meta, dtype)  # host-only; also validates the path list
         self._torch_config = None
+        self.torch_config  # built now: a traced program reads it as a constant and must not run the encoder
 
     @property
     def torch_config(self) -> str:
@@ -144,6 +145,12 @@ class LunaTPUVUConv:
     def uses_compiled_patterns(self) -> bool:
         """Whether the backward kernel with compiled-in coupling patterns applies."""
         return self._plan.query(6) > 0
+
+    @property
+    def backward_variant(self) -> str:
+        """Which first-order backward kernel aligned inputs get: ``generic`` (table-driven), ``tables`` (staged,
+        path list read from tables), ``row``, ``units`` or ``team`` (compiled-in coupling patterns)."""
+        return ("generic", "tables", "row", "units", "team")[self._plan.query(7)]
 
     def check_status(self, device=None) -> None:
         """Raise ``RuntimeError`` if a kernel of this operator gave up a bounded wait since the last check.

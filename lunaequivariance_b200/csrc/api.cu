@@ -66,6 +66,7 @@ extern "C" int64_t luna_uvu_plan_query(const luna_uvu_plan* plan, int what) {
     case LUNA_PLAN_BWD_SMEM_BYTES: return fast_smem_bytes(plan, 1);
     case LUNA_PLAN_CANONICAL_L2: return plan->fast_ok ? plan->fast.canon_l2 : -1;
     case LUNA_PLAN_SPARSE_TERMS: return plan->fast_ok ? plan->fast.sparse_terms : 0;
+    case LUNA_PLAN_BWD_VARIANT: return fast_bwd_variant(plan);
     default: return -1;
   }
 }

@@ -312,16 +312,28 @@ void analyse_fast(luna_uvu_plan* plan) {
     cpl = ch % 128 == 0 ? 4 : (ch % 64 == 0 ? 2 : 1);
   else
     cpl = ch % 64 == 0 ? 2 : 1;
-  if (const char* knob = std::getenv("LUNA_B200_CPL")) {  // tuning knob: cap the channels per lane
-    const int cap = std::atoi(knob);
-    while (cap >= 1 && cpl > cap) cpl /= 2;
-  }
   if (!fill_layout(plan, f, cpl)) return;
   plan->fast = f;
   plan->fast_ok = true;
 }
 
 }  // namespace
+
+Tuning tuning_from_environment() {
+  Tuning t;
+  auto number = [](const char* name) -> long long {
+    const char* value = std::getenv(name);
+    return value ? std::atoll(value) : 0;
+  };
+  t.no_canon = std::getenv("LUNA_B200_NO_CANON") != nullptr;
+  t.no_sparse = std::getenv("LUNA_B200_NO_SPARSE") != nullptr;
+  if (const char* kind = std::getenv("LUNA_B200_BWD_KERNEL"))
+    t.bwd_kernel = kind[0] == 'r' ? 1 : (kind[0] == 'u' ? 2 : (kind[0] == 't' ? 3 : 0));
+  t.max_warps = static_cast<int>(std::max(0ll, number("LUNA_B200_MAXW")));
+  t.row_stages = static_cast<int>(std::max(0ll, number("LUNA_B200_ROW_STAGES")));
+  t.edges_per_warp = std::max(0ll, number("LUNA_B200_EPW"));
+  return t;
+}
 
 int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   int device = 0;
@@ -473,6 +485,7 @@ extern "C" int luna_uvu_plan_create(const luna_uvu_desc* desc, luna_uvu_plan** o
     return fail(LUNA_ERR_INVALID_ARGUMENT, "term arrays missing");
 
   auto plan = new luna_uvu_plan();
+  plan->tuning = tuning_from_environment();
   plan->dtype = desc->dtype;
   plan->X = desc->in1_dim;
   plan->Y = desc->in2_dim;

@@ -101,6 +101,23 @@ struct FastMeta {
 };
 
 // ------------------------------------------------------------------------------------------------ the plan
+// Settings that select kernel variants or override a launch policy.  They come from LUNA_B200_* environment
+// variables, read once when the plan is created (never on a launch path):
+//   LUNA_B200_NO_CANON=1        canonical path lists run the kernels that loop over run-time path tables
+//   LUNA_B200_NO_SPARSE=1       backward without the compiled-in coupling patterns
+//   LUNA_B200_BWD_KERNEL=row|units|team   data-movement variant of the backward kernel with compiled-in patterns
+//   LUNA_B200_MAXW=n            cap on warps per CTA
+//   LUNA_B200_ROW_STAGES=n      cap on weight-row stages of the row-staged backward
+//   LUNA_B200_EPW=n             target edges per warp when a graph needs several waves
+struct Tuning {
+  bool no_canon = false, no_sparse = false;
+  int bwd_kernel = 0;  // 0 automatic, 1 row stages, 2 unit ring, 3 warp teams
+  int max_warps = 0;   // 0: no cap
+  int row_stages = 0;  // 0: no cap
+  int64_t edges_per_warp = 0;  // 0: the kernel's default
+};
+Tuning tuning_from_environment();
+
 struct DeviceTables {
   void* buffer = nullptr;  // one allocation holding every table
   size_t bytes = 0;
@@ -145,6 +162,7 @@ struct luna_uvu_plan {
 
   bool fast_ok = false;
   bool force_generic = false;
+  luna::Tuning tuning{};
   luna::FastMeta fast{};
   std::vector<double> ell_c;
   std::vector<unsigned char> ell_j;
@@ -200,6 +218,8 @@ int generic_contract(luna_uvu_plan* plan, const luna_graph* graph, int free_slot
 
 // Staged kernels (bulk-copy pipeline).  fast_available() is false in a build without them.
 bool fast_available();
+// The luna_bwd_variant the first-order backward takes for this plan (for aligned operands).
+int fast_bwd_variant(const luna_uvu_plan* plan);
 // which: 0 forward-shaped kernel, 1 backward-shaped kernel.  Dynamic shared memory per block, 0 if not eligible.
 int64_t fast_smem_bytes(const luna_uvu_plan* plan, int which);
 int64_t fast_scratch_bytes(const luna_uvu_plan* plan, int64_t num_nodes, int64_t num_edges);

@@ -6,9 +6,16 @@
 //   Y_{l,m}    = a(l,m) y Y_{l-1,m-1} - b(l,m) r^2 Y_{l-2,m-2}          (2 <= m <= 2l-2)
 // is evaluated on a number type: plain scalars for the values, value+gradient numbers for the first derivative,
 // and a directional tangent of value+gradient numbers for the second-order outputs.  Normalisation of the input
-// vector (division by max(|v|, 1e-12)) is part of the differentiated chain.  Coefficients are folded at compile
-// time.  Rows of g / out are staged through shared memory so that global traffic is coalesced.
+// vector (division by max(|v|, 1e-12)) is part of the differentiated chain.  Rows of g / out are staged through
+// shared memory so that global traffic is coalesced.
+//
+// Two evaluators.  The common request - every degree 0..lmax once, lmax <= 6 - runs kernels unrolled for that lmax:
+// the recurrence keeps two levels in registers (level l is written over level l-2, highest component first), its
+// coefficients are immediates, and the output width is a compile-time constant, so the staging loops have no
+// divisions.  Any other degree list (gaps, repeats, lmax up to 12) runs the same recurrence as a run-time loop over
+// three rotating level buffers, which the compiler keeps in local memory.
 #include <algorithm>
+#include <type_traits>
 
 #include "common.h"
 
@@ -170,6 +177,47 @@ __device__ __forceinline__ void walk(int lmax, const N& one, const N& x, const N
     i1 = i0;
     i0 = t;
   }
+}
+
+// ---- unrolled recurrence for the degree list 0..LMAX ------------------------------------------------------------
+template <int I, int N, typename F>
+__device__ __forceinline__ void unroll(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    unroll<I + 1, N>(f);
+  }
+}
+
+// Levels of equal parity share an array: level l is computed from level l-1 (the other array) and level l-2 (its own
+// array) and written over the latter from the highest component down, so no third buffer is needed and every index
+// is a compile-time constant: the arrays live in registers.
+template <typename T, typename N, int LMAX, typename Sink>
+__device__ __forceinline__ void walk_unrolled(const N& one, const N& x, const N& y, const N& z, const N& r2, Sink& sink) {
+  constexpr int kW = 2 * LMAX + 1;
+  N even[kW], odd[kW];
+  even[0] = one;
+  sink.emit(std::integral_constant<int, 0>{}, even);
+  if constexpr (LMAX >= 1) {
+    odd[0] = nscale(T(coef_diag(1)), x);
+    odd[1] = nscale(T(coef_diag(1)), y);
+    odd[2] = nscale(T(coef_diag(1)), z);
+    sink.emit(std::integral_constant<int, 1>{}, odd);
+  }
+  unroll<2, LMAX + 1>([&](auto lc) {
+    constexpr int l = decltype(lc)::value;
+    N* cur = (l % 2 == 0) ? even : odd;        // holds level l-2 on entry
+    const N* p1 = (l % 2 == 0) ? odd : even;   // level l-1
+    unroll<0, 2 * l - 3>([&](auto dc) {        // interior components m = 2l-2 ... 2
+      constexpr int m = 2 * l - 2 - decltype(dc)::value;
+      cur[m] = nsub(nscale(T(coef_a(l, m)), nmul(y, p1[m - 1])), nscale(T(coef_b(l, m)), nmul(r2, cur[m - 2])));
+    });
+    constexpr T edge = T(coef_edge(l)), diag = T(coef_diag(l));
+    cur[0] = nscale(edge, nadd(nmul(p1[0], z), nmul(p1[2 * l - 2], x)));
+    cur[2 * l] = nscale(edge, nsub(nmul(p1[2 * l - 2], z), nmul(p1[0], x)));
+    cur[1] = nscale(diag, nmul(y, p1[0]));
+    cur[2 * l - 1] = nscale(diag, nmul(y, p1[2 * l - 2]));
+    sink.emit(lc, cur);
+  });
 }
 
 template <typename T>
@@ -338,10 +386,171 @@ sh_kernel(const ShParams P, const T* __restrict__ v, const T* __restrict__ g, co
   }
 }
 
+// Sinks of the unrolled kernels: the degree list is 0..LMAX, so degree l starts at column l * l.
+template <typename T>
+struct CanonForwardSink {
+  int normalization;
+  T* row;
+  template <int L>
+  __device__ __forceinline__ void emit(std::integral_constant<int, L>, const T* level) {
+    const T scale = degree_scale<T>(L, normalization);
+#pragma unroll
+    for (int m = 0; m < 2 * L + 1; ++m) row[L * L + m] = scale * level[m];
+  }
+};
+template <typename T>
+struct CanonBackwardSink {
+  int normalization;
+  const T* row;
+  T dx = T(0), dy = T(0), dz = T(0);
+  template <int L>
+  __device__ __forceinline__ void emit(std::integral_constant<int, L>, const G3<T>* level) {
+    const T scale = degree_scale<T>(L, normalization);
+#pragma unroll
+    for (int m = 0; m < 2 * L + 1; ++m) {
+      const T gsum = scale * row[L * L + m];
+      dx += gsum * level[m].x;
+      dy += gsum * level[m].y;
+      dz += gsum * level[m].z;
+    }
+  }
+};
+template <typename T>
+struct CanonDoubleSink {
+  int normalization;
+  T* row;  // g row on entry; overwritten with sg
+  bool write_sg;
+  T sx = T(0), sy = T(0), sz = T(0);
+  template <int L>
+  __device__ __forceinline__ void emit(std::integral_constant<int, L>, const Du<G3<T>>* level) {
+    const T scale = degree_scale<T>(L, normalization);
+#pragma unroll
+    for (int m = 0; m < 2 * L + 1; ++m) {
+      const T gsum = scale * row[L * L + m];
+      sx += gsum * level[m].b.x;
+      sy += gsum * level[m].b.y;
+      sz += gsum * level[m].b.z;
+      if (write_sg) row[L * L + m] = scale * level[m].b.v;
+    }
+  }
+};
+
+// Same three modes as sh_kernel for the degree list 0..LMAX, everything about the list known at compile time.
+template <typename T, int MODE, int LMAX>
+__global__ void __launch_bounds__(kBlock)
+sh_canon_kernel(const ShParams P, const T* __restrict__ v, const T* __restrict__ g, const T* __restrict__ rx,
+                T* __restrict__ out0, T* __restrict__ out1, int64_t n) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* smem = reinterpret_cast<T*>(smem_raw);
+  constexpr int C = (LMAX + 1) * (LMAX + 1), CP = C | 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T* tile = smem + static_cast<size_t>(warp) * 32 * CP;
+  T* row = tile + lane * CP;
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (kBlock / 32);
+  for (int64_t base = (static_cast<int64_t>(blockIdx.x) * (kBlock / 32) + warp) * 32; base < n;
+       base += warps_total * 32) {
+    const int rows = (n - base < 32) ? static_cast<int>(n - base) : 32;
+    const int64_t item = base + lane;
+    const bool active = lane < rows;
+    T vx = T(0), vy = T(1), vz = T(0);
+    if (active) {
+      vx = v[item * 3 + 0];
+      vy = v[item * 3 + 1];
+      vz = v[item * 3 + 2];
+    }
+    if constexpr (MODE != 0) {
+      const T* gsrc = g + base * C;
+#pragma unroll 4
+      for (int idx = lane; idx < rows * C; idx += 32) tile[(idx / C) * CP + (idx % C)] = gsrc[idx];
+      __syncwarp();
+    }
+    if constexpr (MODE == 0) {
+      T x = vx, y = vy, z = vz, r2;
+      prepare<T, T>(P, x, y, z, r2);
+      CanonForwardSink<T> sink{P.normalization, row};
+      walk_unrolled<T, T, LMAX>(T(1), x, y, z, r2, sink);
+      __syncwarp();
+      T* dst = out0 + base * C;
+#pragma unroll 4
+      for (int idx = lane; idx < rows * C; idx += 32) dst[idx] = tile[(idx / C) * CP + (idx % C)];
+    } else if constexpr (MODE == 1) {
+      using N = G3<T>;
+      N x{vx, T(1), T(0), T(0)}, y{vy, T(0), T(1), T(0)}, z{vz, T(0), T(0), T(1)}, r2;
+      prepare<T, N>(P, x, y, z, r2);
+      CanonBackwardSink<T> sink{P.normalization, row};
+      walk_unrolled<T, N, LMAX>(N{T(1), T(0), T(0), T(0)}, x, y, z, r2, sink);
+      if (active) {
+        out0[item * 3 + 0] = sink.dx;
+        out0[item * 3 + 1] = sink.dy;
+        out0[item * 3 + 2] = sink.dz;
+      }
+    } else {
+      using N = Du<G3<T>>;
+      T tx = T(0), ty = T(0), tz = T(0);
+      if (active) {
+        tx = rx[item * 3 + 0];
+        ty = rx[item * 3 + 1];
+        tz = rx[item * 3 + 2];
+      }
+      const G3<T> zero{T(0), T(0), T(0), T(0)};
+      N x{{vx, T(1), T(0), T(0)}, {tx, T(0), T(0), T(0)}};
+      N y{{vy, T(0), T(1), T(0)}, {ty, T(0), T(0), T(0)}};
+      N z{{vz, T(0), T(0), T(1)}, {tz, T(0), T(0), T(0)}};
+      N r2;
+      prepare<T, N>(P, x, y, z, r2);
+      CanonDoubleSink<T> sink{P.normalization, row, out1 != nullptr};
+      walk_unrolled<T, N, LMAX>(N{{T(1), T(0), T(0), T(0)}, zero}, x, y, z, r2, sink);
+      if (active && out0 != nullptr) {
+        out0[item * 3 + 0] = sink.sx;
+        out0[item * 3 + 1] = sink.sy;
+        out0[item * 3 + 2] = sink.sz;
+      }
+      if (out1 != nullptr) {
+        __syncwarp();
+        T* dst = out1 + base * C;
+#pragma unroll 4
+        for (int idx = lane; idx < rows * C; idx += 32) dst[idx] = tile[(idx / C) * CP + (idx % C)];
+      }
+    }
+    __syncwarp();
+  }
+}
+
+template <typename T, int MODE, int LMAX>
+int launch_canon(const ShParams& P, const T* v, const T* g, const T* rx, T* out0, T* out1, int64_t n,
+                 cudaStream_t stream) {
+  constexpr int C = (LMAX + 1) * (LMAX + 1);
+  const size_t smem = static_cast<size_t>(kBlock / 32) * 32 * (C | 1) * sizeof(T);
+  auto kernel = sh_canon_kernel<T, MODE, LMAX>;
+  if (smem > 48 * 1024)
+    LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  const int64_t blocks = std::min<int64_t>(ceil_div(n, kBlock), 148 * 16);
+  kernel<<<static_cast<unsigned>(blocks), kBlock, smem, stream>>>(P, v, g, rx, out0, out1, n);
+  LUNA_LAUNCH_CHECK("spherical harmonics (degrees 0..lmax)");
+  return LUNA_OK;
+}
+
+// True if the degree list is 0, 1, ..., lmax, each once and in that order.
+inline bool is_canonical_list(const ShParams& P, int lmax) {
+  for (int l = 0; l <= lmax; ++l)
+    if (P.count[l] != 1 || P.column[l][0] != l * l) return false;
+  return true;
+}
+
 template <typename T, int MODE>
 int launch_lmax(int lmax, ShParams P, const T* v, const T* g, const T* rx, T* out0, T* out1, int64_t n,
                 cudaStream_t stream) {
   P.lmax = lmax;
+  if (lmax >= 1 && lmax <= 6 && is_canonical_list(P, lmax)) {
+    switch (lmax) {
+      case 1: return launch_canon<T, MODE, 1>(P, v, g, rx, out0, out1, n, stream);
+      case 2: return launch_canon<T, MODE, 2>(P, v, g, rx, out0, out1, n, stream);
+      case 3: return launch_canon<T, MODE, 3>(P, v, g, rx, out0, out1, n, stream);
+      case 4: return launch_canon<T, MODE, 4>(P, v, g, rx, out0, out1, n, stream);
+      case 5: return launch_canon<T, MODE, 5>(P, v, g, rx, out0, out1, n, stream);
+      default: return launch_canon<T, MODE, 6>(P, v, g, rx, out0, out1, n, stream);
+    }
+  }
   const size_t smem = static_cast<size_t>(kBlock / 32) * 32 * (P.C | 1) * sizeof(T);
   auto kernel = sh_kernel<T, MODE>;
   if (smem > 48 * 1024)

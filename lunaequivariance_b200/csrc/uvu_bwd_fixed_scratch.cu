@@ -7,9 +7,12 @@
 // is not acceptable, or a process whose memory pool was sized up front and is closed.  For them the partial rows
 // live in a fixed array that is part of the library image.
 //
-// What it costs.  The array below takes kFixedScratchBytes of device memory on every GPU that loads the library,
-// from load until the process exits, whether or not this entry point is ever called.  Requests that need more are
-// refused.  All calls on a device share the one array and it keeps whatever the previous call left in it: the
+// What it costs.  The array below takes kFixedScratchBytes of device memory on a GPU from the moment this part of
+// the library is loaded there until the process exits.  With the CUDA runtime's default lazy loading that moment
+// is luna_uvu_conv_noalloc_prepare (the set-up call, which looks the array up); with eager loading it is the
+// creation of the context.  Either way it is never the hot call: luna_uvu_conv_bwd_noalloc refuses to run on a
+// device that has not been prepared.  Requests that need more than the array are refused.  All calls on a device
+// share the one array and it keeps whatever the previous call left in it: the
 // backward kernel overwrites every partial row it later reads, so nothing has to be cleared, but two calls that
 // run at the same time on one GPU (different streams, or different host threads) would overwrite each other's
 // partial rows.  Keep calls to this entry point on one device in stream order.
@@ -29,14 +32,21 @@ static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchByte
 std::mutex g_setup_mutex;
 void* g_device_address[kMaxDevices] = {};
 
-// Resolves the array's address on the current device, once per device.  Allocates nothing, but the first call on a
-// device may make the runtime load this module there, so it belongs before any stream capture.
-int fixed_scratch_address(void** out) {
-  int device = 0;
-  LUNA_CUDA_CHECK(cudaGetDevice(&device));
-  if (device < 0 || device >= kMaxDevices)
-    return luna::fail(LUNA_ERR_UNSUPPORTED, "device ordinal %d is beyond the %d this entry point tracks", device,
+int current_device(int* device) {
+  LUNA_CUDA_CHECK(cudaGetDevice(device));
+  if (*device < 0 || *device >= kMaxDevices)
+    return luna::fail(LUNA_ERR_UNSUPPORTED, "device ordinal %d is beyond the %d this entry point tracks", *device,
                       kMaxDevices);
+  return LUNA_OK;
+}
+
+// Set-up: resolves the array's address on the current device, once per device.  This is where the runtime may load
+// this module onto the device (and the array starts to occupy memory), so it belongs before any stream capture and
+// outside the part of the program that must not allocate.
+int resolve_fixed_scratch() {
+  int device = 0;
+  int rc = current_device(&device);
+  if (rc != LUNA_OK) return rc;
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (g_device_address[device] == nullptr) {
     void* address = nullptr;
@@ -44,6 +54,16 @@ int fixed_scratch_address(void** out) {
     if (address == nullptr) return luna::fail(LUNA_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
     g_device_address[device] = address;
   }
+  return LUNA_OK;
+}
+
+// The address resolved by the set-up call, or null if this device has not been prepared.  Touches no CUDA state
+// beyond asking which device is current.
+int fixed_scratch_address(void** out) {
+  int device = 0;
+  int rc = current_device(&device);
+  if (rc != LUNA_OK) return rc;
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
   *out = g_device_address[device];
   return LUNA_OK;
 }
@@ -62,13 +82,26 @@ int plan_is_resident(luna_uvu_plan* plan, bool* resident) {
 
 extern "C" int64_t luna_uvu_conv_noalloc_max_scratch_bytes(void) { return kFixedScratchBytes; }
 
+extern "C" int luna_uvu_conv_noalloc_prepare(luna_uvu_plan* plan) {
+  luna::clear_error();
+  if (!plan) return luna::fail(LUNA_ERR_INVALID_ARGUMENT, "null plan");
+  int rc = resolve_fixed_scratch();
+  if (rc != LUNA_OK) return rc;
+  const luna::DeviceTables* tables = nullptr;
+  return luna::get_device_tables(plan, &tables);  // uploads the plan's lookup tables (one cudaMalloc) if needed
+}
+
 extern "C" int luna_uvu_conv_bwd_noalloc(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,
                                          const void* w, const void* g, void* gx, void* gy, void* gw, void* stream) {
   luna::clear_error();
   if (!plan) return luna::fail(LUNA_ERR_INVALID_ARGUMENT, "null plan");
   if (!graph) return luna::fail(LUNA_ERR_INVALID_ARGUMENT, "null graph");
-  const int64_t need = luna_uvu_conv_scratch_bytes(plan, graph->num_nodes, graph->num_edges);
-  if (need < 0) return luna::fail(LUNA_ERR_INVALID_ARGUMENT, "negative graph size");
+  if (graph->num_nodes < 0 || graph->num_edges < 0) return luna::fail(LUNA_ERR_INVALID_ARGUMENT, "negative graph size");
+  // nothing to compute (only gx rows to clear): no scratch, no tables
+  if (graph->num_nodes == 0 || graph->num_edges == 0)
+    return luna_uvu_conv_bwd(plan, graph, x, y, w, g, gx, gy, gw, nullptr, 0, stream);
+  // Only the edge-attribute gradient goes through partial rows; without it no scratch is used at all.
+  const int64_t need = gy ? luna_uvu_conv_scratch_bytes(plan, graph->num_nodes, graph->num_edges) : 0;
   if (need > kFixedScratchBytes)
     return luna::fail(LUNA_ERR_SCRATCH,
                       "this graph needs %lld bytes of scratch but the built-in array holds %lld: use "
@@ -77,13 +110,13 @@ extern "C" int luna_uvu_conv_bwd_noalloc(luna_uvu_plan* plan, const luna_graph* 
   bool resident = false;
   int rc = plan_is_resident(plan, &resident);
   if (rc != LUNA_OK) return rc;
-  if (!resident)
-    return luna::fail(LUNA_ERR_INVALID_ARGUMENT,
-                      "the plan's tables are not on this device yet and uploading them would allocate: call "
-                      "luna_uvu_check_status (or any other entry point) with this plan on this device once, at "
-                      "set-up time");
   void* scratch = nullptr;
   rc = fixed_scratch_address(&scratch);
   if (rc != LUNA_OK) return rc;
+  if (!resident || scratch == nullptr)
+    return luna::fail(LUNA_ERR_INVALID_ARGUMENT,
+                      "this plan and device have not been prepared: the plan's tables are not on this device yet or "
+                      "the built-in array has not been looked up, and doing either here could allocate.  Call "
+                      "luna_uvu_conv_noalloc_prepare(plan) once per plan and device at set-up time");
   return luna_uvu_conv_bwd(plan, graph, x, y, w, g, gx, gy, gw, scratch, kFixedScratchBytes, stream);
 }

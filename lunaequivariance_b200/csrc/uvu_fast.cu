@@ -9,11 +9,7 @@ namespace fastk {
 
 Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_bytes, int max_smem_optin,
                            int regs_per_thread, int max_warps, int min_depth, int max_depth) {
-  int max_ctas = 4;
-  if (const char* knob = std::getenv("LUNA_B200_MAX_CTAS")) max_ctas = std::max(1, std::atoi(knob));
-  if (const char* knob = std::getenv("LUNA_B200_DEPTH")) max_depth = std::max(min_depth, std::min(max_depth, std::atoi(knob)));
-  if (const char* knob = std::getenv("LUNA_B200_MAXW")) max_warps = std::max(1, std::min(max_warps, std::atoi(knob)));
-  if (const char* knob = std::getenv("LUNA_B200_MIN_DEPTH")) min_depth = std::max(min_depth, std::min(max_depth, std::atoi(knob)));
+  const int max_ctas = 4;
   const int regs_per_warp = (std::max(regs_per_thread, 1) + 7) / 8 * 8 * 32;
   const int warp_slots = std::max(1, 16384 / regs_per_warp);  // per sub-partition
   Residency best;
@@ -48,7 +44,7 @@ Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_
 int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count) {
   const int64_t wave = static_cast<int64_t>(sm_count) * r.ctas;  // CTAs resident at once
   const int64_t wave_warps = wave * r.warps;
-  const int64_t per_warp = edges_per_warp(target);
+  const int64_t per_warp = target;
   if (num_edges > per_warp * wave_warps) {  // several waves of about `target` edges per warp, whole waves only
     const int64_t blocks = ceil_div(ceil_div(num_edges, per_warp), r.warps);
     return ceil_div(blocks, wave) * wave;
@@ -77,6 +73,34 @@ extern template int launch_fast_bwd<double, 2>(LUNA_BWD_SIG(double));
 }  // namespace fastk
 
 bool fast_available() { return true; }
+
+namespace fastk {
+bool team_available() { return true; }
+}  // namespace fastk
+
+int fast_bwd_variant(const luna_uvu_plan* plan) {
+  using fastk::team_available;
+  if (!plan->fast_ok || plan->force_generic) return LUNA_BWD_TABLE_DRIVEN;
+  const FastMeta& f = plan->fast;
+  const int lx = f.LX, lo = f.LO, l2 = f.canon_l2;
+  // shapes with kernels unrolled for the canonical full path list (see launch_fast_bwd)
+  const bool compiled_shape = !plan->tuning.no_canon && ((lx == 2 && l2 == 3 && lo == 3) || (lx == 2 && l2 == 2 && lo == 2) ||
+                                                         (lx == 3 && l2 == 3 && lo == 3) || (lx == 1 && l2 == 1 && lo == 1));
+  if (!compiled_shape || f.sparse_terms <= 0 || plan->tuning.no_sparse) return LUNA_BWD_STAGED_TABLES;
+  const size_t elem = plan->dtype == LUNA_F64 ? 8 : 4;
+  // Warp teams: 128 FP32 channels, two warps of 64 channels share an edge's staged rows.
+  const bool team_ok = team_available() && plan->dtype == LUNA_F32 && f.ch == 128 && f.chunks == 1;
+  // Row stages pay off when an edge's weight row is one long contiguous piece for the CTA; short rows and rows
+  // split into channel chunks go through the unit ring.
+  const bool rows_ok = f.chunks == 1;
+  int variant = team_ok ? LUNA_BWD_WARP_TEAMS
+                        : (rows_ok && static_cast<size_t>(f.w_stage_elems) * elem >= 2560 ? LUNA_BWD_ROW_STAGES
+                                                                                          : LUNA_BWD_UNIT_RING);
+  if (plan->tuning.bwd_kernel == 1) variant = LUNA_BWD_ROW_STAGES;
+  if (plan->tuning.bwd_kernel == 2) variant = LUNA_BWD_UNIT_RING;
+  if (plan->tuning.bwd_kernel == 3 && team_ok) variant = LUNA_BWD_WARP_TEAMS;
+  return variant;
+}
 
 namespace {
 constexpr int kSmemLimit = 227 * 1024;

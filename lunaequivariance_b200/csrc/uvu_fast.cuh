@@ -15,6 +15,7 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstdlib>
 #include <type_traits>
@@ -217,13 +218,13 @@ Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_
 // CTAs to launch: about `target` edges per warp, rounded up to whole waves of resident CTAs.
 int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count);
 
-// Target edges per warp when sizing the grid (tuning knob LUNA_B200_EPW).
-inline int64_t edges_per_warp(int64_t fallback) {
-  if (const char* knob = std::getenv("LUNA_B200_EPW")) {
-    const long long v = std::atoll(knob);
-    if (v > 0) return v;
-  }
-  return fallback;
+// Target edges per warp when sizing the grid: the plan's override if it has one.
+inline int64_t edges_per_warp(const Tuning& tuning, int64_t fallback) {
+  return tuning.edges_per_warp > 0 ? tuning.edges_per_warp : fallback;
+}
+// A kernel's warp limit under the plan's cap.
+inline int capped_warps(const Tuning& tuning, int max_warps) {
+  return tuning.max_warps > 0 ? std::max(1, std::min(max_warps, tuning.max_warps)) : max_warps;
 }
 
 // ---- canonical path lists ---------------------------------------------------------------------------------------

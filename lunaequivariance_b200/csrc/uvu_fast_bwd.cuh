@@ -56,6 +56,7 @@ struct BwdParams {
   int64_t num_src_nodes, num_edges;
   int slots;
   int row_stages;  // kernel with compiled-in patterns: weight-row stages per warp
+  int64_t tile_nodes;  // warp-team kernel: source nodes per tile
   int acc_x, acc_y, acc_w;
 };
 
@@ -528,6 +529,11 @@ __global__ void reduce_gy_partial(const T* __restrict__ partial, T* __restrict__
 namespace luna {
 namespace fastk {
 
+// Warp-team kernel (uvu_fast_bwd_team.cuh), FP32 with 128 channels; compiled in its own translation unit, which
+// dispatches on the degree shape of the canonical path list.
+int launch_fast_bwd_team_f32(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph,
+                             const BwdParams<float>& P, bool has_gy, bool wxw, cudaStream_t stream);
+
 template <typename T, int CPL, int LX, int LO, int L2>
 int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
                         const T* y, const T* w, const T* g, T* gx, bool acc_x, T* gy, bool acc_y, T* gw, bool acc_w,
@@ -550,6 +556,7 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.sp_c = nullptr;
   P.sp_j = nullptr;
   P.row_stages = 0;
+  P.tile_nodes = 1;
   P.status = dt.status;
   P.num_src_nodes = graph->num_src_nodes > 0 ? graph->num_src_nodes : graph->num_nodes;
   P.num_edges = graph->num_edges;
@@ -575,11 +582,16 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   if constexpr (L2 >= 0) {
     // compiled-in coupling patterns, if the plan's terms have them
     if constexpr (sparse_shape_ok<LX, (L2 < 0 ? 0 : L2), LO>()) {
-      if (f.sparse_terms > 0 && std::getenv("LUNA_B200_NO_SPARSE") == nullptr) {
-        // Row stages pay off when an edge's weight row is one long contiguous piece for this CTA; short rows and
-        // rows split into channel chunks go through the unit ring (LUNA_B200_BWD_KERNEL=row|units overrides).
-        bool rows = f.chunks == 1 && static_cast<size_t>(f.w_stage_elems) * sizeof(T) >= 2560;
-        if (const char* knob = std::getenv("LUNA_B200_BWD_KERNEL")) rows = knob[0] == 'r';
+      const int variant = fast_bwd_variant(plan);
+      if constexpr (std::is_same<T, float>::value) {
+        if (variant == LUNA_BWD_WARP_TEAMS) {
+          const int rc = launch_fast_bwd_team_f32(plan, dt, graph, P, gy != nullptr, wxw, stream);
+          if (rc != LUNA_OK) return rc;
+          launched = true;
+        }
+      }
+      if (variant == LUNA_BWD_ROW_STAGES || variant == LUNA_BWD_UNIT_RING) {
+        const bool rows = variant == LUNA_BWD_ROW_STAGES;
         const int rc = rows ? launch_fast_bwd_sparse<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream)
                             : launch_fast_bwd_units<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream);
         if (rc != LUNA_OK) return rc;
@@ -600,7 +612,7 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
     // between two units and two edges in a warp's ring
     const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), bwd_fixed_bytes<T, CPL>(f),
-                                         bwd_shared_bytes(f), dt.max_smem_optin, attr.numRegs, MAXW, 2,
+                                         bwd_shared_bytes(f), dt.max_smem_optin, attr.numRegs, capped_warps(plan->tuning, MAXW), 2,
                                          std::min(kMaxSlots, 2 * f.nkinds));
     if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
     P.slots = r.depth;
@@ -609,7 +621,7 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
     // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
     LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-    const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
+    const int64_t blocks = grid_blocks(graph->num_edges, edges_per_warp(plan->tuning, 1024), r, dt.sm_count);
     const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
     kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
     LUNA_LAUNCH_CHECK("staged backward");
@@ -628,7 +640,7 @@ int launch_fast_bwd(const luna_uvu_plan* plan, const DeviceTables& dt, const lun
                     void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
   const int lx = plan->fast.LX, lo = plan->fast.LO, l2 = plan->fast.canon_l2;
 #define LUNA_BWD_ARGS plan, dt, graph, x, y, w, g, gx, acc_x, gy, acc_y, gw, acc_w, scratch, scratch_bytes, stream
-  if (std::getenv("LUNA_B200_NO_CANON") == nullptr) {
+  if (!plan->tuning.no_canon) {
     if (lx == 2 && l2 == 3 && lo == 3) return launch_fast_bwd_one<T, CPL, 2, 3, 3>(LUNA_BWD_ARGS);
     if (lx == 2 && l2 == 2 && lo == 2) return launch_fast_bwd_one<T, CPL, 2, 2, 2>(LUNA_BWD_ARGS);
     if (lx == 3 && l2 == 3 && lo == 3) return launch_fast_bwd_one<T, CPL, 3, 3, 3>(LUNA_BWD_ARGS);

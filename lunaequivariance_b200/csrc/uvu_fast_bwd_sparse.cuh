@@ -100,13 +100,19 @@ __device__ __forceinline__ void reduce_tile_rows(const T* red, T* out, int lane)
 
 // Warps per CTA at most (caps the registers per thread): FP32 with at most two channels per lane needs fewer
 // registers and runs up to 12 warps (168 registers), everything else 8 (255).
-template <typename T, int CPL>
+#ifndef LUNA_SPARSE_WARPS_SMALL
+#define LUNA_SPARSE_WARPS_SMALL 12
+#endif
+// Shapes up to degree 2 keep far less state per lane (9 x and gx packets, 9 gy accumulators, a short program);
+// LUNA_SPARSE_WARPS_SMALL is their warp limit.
+template <typename T, int CPL, int LX = 3, int L2 = 3, int LO = 3>
 __host__ __device__ constexpr int sparse_max_warps() {
-  return (sizeof(T) == 4 && CPL <= 2) ? 12 : 8;
+  if (sizeof(T) == 4 && CPL <= 2) return (LX <= 2 && L2 <= 2 && LO <= 2) ? LUNA_SPARSE_WARPS_SMALL : 12;
+  return 8;
 }
 
 template <typename T, int CPL, int LX, int L2, int LO, bool WXW, bool WY>
-__global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_sparse_kernel(const __grid_constant__ BwdParams<T> P) {
+__global__ void __launch_bounds__(sparse_max_warps<T, CPL, LX, L2, LO>() * 32, 1) fast_bwd_sparse_kernel(const __grid_constant__ BwdParams<T> P) {
   using PK = Pk<T, CPL>;
   using V = typename PK::V;
   constexpr int NP = PK::NP;
@@ -514,10 +520,10 @@ int launch_fast_bwd_sparse(const luna_uvu_plan* plan, const DeviceTables& dt, co
   Residency r;
   int row_stages = 0;
   {
-    int max_warps = std::min(sparse_max_warps<T, CPL>(), 65536 / (std::max(attr.numRegs, 1) * 32));
-    if (const char* knob = std::getenv("LUNA_B200_MAXW")) max_warps = std::max(1, std::min(max_warps, std::atoi(knob)));
+    int max_warps = std::min(sparse_max_warps<T, CPL, LX, L2, LO>(), 65536 / (std::max(attr.numRegs, 1) * 32));
+    max_warps = capped_warps(plan->tuning, max_warps);
     int max_stages = kMaxRowStages;
-    if (const char* knob = std::getenv("LUNA_B200_ROW_STAGES")) max_stages = std::max(2, std::min(max_stages, std::atoi(knob)));
+    if (plan->tuning.row_stages > 0) max_stages = std::max(2, std::min(max_stages, plan->tuning.row_stages));
     const size_t budget = static_cast<size_t>(dt.max_smem_optin);
     for (int w = max_warps; w >= 1 && r.depth == 0; --w)
       for (int st = max_stages; st >= 2 && r.depth == 0; --st)
@@ -537,7 +543,7 @@ int launch_fast_bwd_sparse(const luna_uvu_plan* plan, const DeviceTables& dt, co
   P.row_stages = row_stages;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(r.block_bytes)));
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-  const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
+  const int64_t blocks = grid_blocks(graph->num_edges, edges_per_warp(plan->tuning, 1024), r, dt.sm_count);
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
   kernel<<<grid, r.warps * 32, r.block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged backward (compiled-in coupling patterns)");

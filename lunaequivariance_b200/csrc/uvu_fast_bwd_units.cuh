@@ -25,7 +25,7 @@ __host__ __device__ inline size_t units_shared_bytes(const FastMeta& f) {
 }
 
 template <typename T, int CPL, int LX, int L2, int LO, bool WXW, bool WY>
-__global__ void __launch_bounds__(sparse_max_warps<T, CPL>() * 32, 1) fast_bwd_units_kernel(const __grid_constant__ BwdParams<T> P) {
+__global__ void __launch_bounds__(sparse_max_warps<T, CPL, LX, L2, LO>() * 32, 1) fast_bwd_units_kernel(const __grid_constant__ BwdParams<T> P) {
   using PK = Pk<T, CPL>;
   using V = typename PK::V;
   constexpr int NP = PK::NP;
@@ -360,13 +360,13 @@ int launch_fast_bwd_units(const luna_uvu_plan* plan, const DeviceTables& dt, con
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
   const Residency r = choose_residency(static_cast<size_t>(f.slot_elems) * sizeof(T), units_fixed_bytes<T>(f),
-                                       units_shared_bytes<T>(f), dt.max_smem_optin, attr.numRegs, sparse_max_warps<T, CPL>(), 2,
+                                       units_shared_bytes<T>(f), dt.max_smem_optin, attr.numRegs, capped_warps(plan->tuning, sparse_max_warps<T, CPL, LX, L2, LO>()), 2,
                                        std::min(kMaxSlots, 2 * f.nkinds));
   if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged backward needs more shared memory than the device has");
   P.slots = r.depth;
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(r.block_bytes)));
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-  const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
+  const int64_t blocks = grid_blocks(graph->num_edges, edges_per_warp(plan->tuning, 1024), r, dt.sm_count);
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
   kernel<<<grid, r.warps * 32, r.block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged backward (compiled-in coupling patterns, unit ring)");

@@ -297,7 +297,7 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   cudaFuncAttributes attr;
   LUNA_CUDA_CHECK(cudaFuncGetAttributes(&attr, kernel));
   const Residency r = choose_residency(stage, fwd_fixed_bytes<T, CPL>(f), ell_bytes<T>(f.m_total, f.m_terms),
-                                       dt.max_smem_optin, attr.numRegs, kFwdMaxWarps, 2, 3);
+                                       dt.max_smem_optin, attr.numRegs, capped_warps(plan->tuning, kFwdMaxWarps), 2, 3);
   if (r.depth == 0) return fail(LUNA_ERR_UNSUPPORTED, "staged forward needs more shared memory than the device has");
   P.stages = r.depth;
   const size_t block_bytes = r.block_bytes;
@@ -305,7 +305,7 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
   // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-  const int64_t blocks = grid_blocks(graph->num_edges, 1024, r, dt.sm_count);
+  const int64_t blocks = grid_blocks(graph->num_edges, edges_per_warp(plan->tuning, 1024), r, dt.sm_count);
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
   kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged forward");
@@ -319,7 +319,7 @@ int launch_fast_fwd(const luna_uvu_plan* plan, const DeviceTables& dt, const lun
                     const T* y, const T* w, T* out, bool accumulate, cudaStream_t stream) {
   const int lx = plan->fast.LX, lo = plan->fast.LO, l2 = plan->fast.canon_l2;
 #define LUNA_FWD_ARGS plan, dt, graph, x, y, w, out, accumulate, stream
-  if (std::getenv("LUNA_B200_NO_CANON") == nullptr) {
+  if (!plan->tuning.no_canon) {
     if (lx == 2 && l2 == 3 && lo == 3) return launch_fast_fwd_one<T, CPL, 2, 3, 3>(LUNA_FWD_ARGS);
     if (lx == 2 && l2 == 2 && lo == 2) return launch_fast_fwd_one<T, CPL, 2, 2, 2>(LUNA_FWD_ARGS);
     if (lx == 3 && l2 == 3 && lo == 3) return launch_fast_fwd_one<T, CPL, 3, 3, 3>(LUNA_FWD_ARGS);

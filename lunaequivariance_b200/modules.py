@@ -120,6 +120,11 @@ class SphericalHarmonics(torch.nn.Module):
         self._dtype_anchor = torch.empty(0, dtype=_checked_sh_dtype(torch.get_default_dtype() if dtype is None else dtype))
         self._config = SphericalHarmonicsConfig(irreps_out, normalize, normalization, self._dtype_anchor.dtype,
                                                 irreps_in=irreps_in)
+        # the kernels evaluate in the dtype of the input, whatever the module's own dtype: one config for each
+        self._by_dtype = {
+            t: SphericalHarmonicsConfig(self._config._ls_list, self._config.normalize, normalization, t,
+                                        irreps_in=str(self._config.irreps_in))
+            for t in (torch.float32, torch.float64)}
         self.last_execution_backend = "uninitialized"
 
     irreps_in = property(lambda self: self._config.irreps_in)
@@ -138,10 +143,7 @@ class SphericalHarmonics(torch.nn.Module):
         return result
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        config = self._config
-        if config.compute_dtype != x.dtype:  # evaluate in the dtype of the input, as the functional form does
-            config = SphericalHarmonicsConfig(config._ls_list, config.normalize, config.normalization, x.dtype,
-                                              irreps_in=str(config.irreps_in))
+        config = self._by_dtype.get(x.dtype, self._config)
         result = spherical_harmonics(config._ls_list, x, config.normalize, config.normalization, config=config)
         self.last_execution_backend = "cuda_fused"
         return result

@@ -62,14 +62,16 @@ class SphericalHarmonicsConfig:
                          out_dim=self.irreps_out.dim)
         self.last_execution_backend = "uninitialized"
         self.backward_backend = None
+        # encoded now: a traced program carries it as a string constant and must not run the encoder
+        self._descriptor = json.dumps([list(self._ls_list), self.normalize, self.normalization, self.index_bits,
+                                       str(self.compute_dtype).removeprefix("torch.")])
 
     @property
     def out_dim(self) -> int:
         return self.meta["out_dim"]
 
     def descriptor(self) -> str:
-        return json.dumps([list(self._ls_list), self.normalize, self.normalization, self.index_bits,
-                           str(self.compute_dtype).removeprefix("torch.")])
+        return self._descriptor
 
     def native(self, dtype) -> "_native.ShDesc":
         if len(self._ls_list) > 32:
@@ -276,5 +278,13 @@ def spherical_harmonics(l, x, normalize, normalization="integral", *, config=Non
     config.backward_backend = "cuda_fused_recompute" if tracked else None
     return SphericalHarmonicsFunction.apply(config, x) if tracked else run_forward(config, x)
 
+
+# The composite op a traced or exported program can carry instead of the Python call; it decomposes into the ops
+# above (same schema as the reference's fragment, ``src/o3/spherical_harmonics/interface.py:242-253``).
+_FRAGMENT = torch.library.Library("lunaeq", "FRAGMENT")
+_FRAGMENT.define("spherical_harmonics(Tensor x, int[] degrees, bool normalize, str normalization) -> Tensor")
+_FRAGMENT.impl("spherical_harmonics",
+               lambda x, degrees, normalize, normalization: spherical_harmonics(degrees, x, normalize, normalization),
+               "CompositeImplicitAutograd")
 
 __all__ = ["spherical_harmonics", "SphericalHarmonicsConfig", "parse_irreps", "UNSET"]

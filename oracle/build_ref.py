@@ -14,7 +14,9 @@ this recipe
    ``TORCH_CUDA_ARCH_LIST=10.0`` (the arch the reference itself would resolve on a B200: it asks torch for the visible
    device's compute capability, ``src/utils/jit.py:154-157``),
 3. copies the resulting ``.so`` files to ``oracle/_ref/`` and writes ``oracle/_ref/manifest.json`` with the few
-   launch facts a caller needs (which graph tables the extension wants, how many partial slabs).
+   launch facts a caller needs (which graph tables the extension wants, how many partial slabs, and up to which
+   node and edge counts the extension's 32-bit index variant is valid: beyond them the reference switches to its
+   64-bit variant, ``src/lunatp/utils/layout.py:441-517``).
 
 No reference source is copied into this repository; the generated ``.cu`` text stays in the build folder under
 ``oracle/_ref/build`` (ignored by git and not shipped to the GPU box).  ``oracle/ref_kernels.py`` loads the libraries
@@ -67,7 +69,7 @@ def main(argv) -> int:
     import_reference(root)
     # load_tp_extension refuses to compile without a visible device; compiling needs none.
     torch.cuda.is_available = lambda: True
-    from LunaEquivariance.lunatp.utils.layout import TensorProductConfig, TensorProductPaths
+    from LunaEquivariance.lunatp.utils.layout import TensorProductConfig, TensorProductPaths, configure_indexing
     from LunaEquivariance.lunatp.uvu_conv.kernels import backward as ref_backward
     from LunaEquivariance.lunatp.uvu_conv.kernels.utils import build_uvu_conv_metadata, configure_uvu_conv
     from LunaEquivariance.o3.irreps import Irreps
@@ -101,6 +103,13 @@ def main(argv) -> int:
             entry = manifest.get(key)
             if entry and entry.get("meta_digest") == digest and all(
                     os.path.exists(os.path.join(OUT, entry[k]["file"])) for k in ("forward", "backward")):
+                if "index_edge_limit" not in entry:  # limits of the 32-bit index variant, from the reference's rule
+                    probe = types.SimpleNamespace()
+                    configure_indexing(probe, meta, "uvu_conv", 32)
+                    entry.update(index_node_limit=int(probe.index_node_limit),
+                                 index_edge_limit=int(probe.index_edge_limit))
+                    with open(manifest_path, "w") as handle:
+                        json.dump(manifest, handle, indent=1, sort_keys=True)
                 print(f"{key}: up to date")
                 continue
             print(f"{key}: building forward", flush=True)
@@ -118,6 +127,7 @@ def main(argv) -> int:
                 meta_digest=digest, dtype=dtype_name, irreps=[in1, in2, out],
                 instructions=[list(i) for i in instructions],
                 in1_dim=op.in1_dim, in2_dim=op.in2_dim, out_dim=op.out_dim, weight_numel=op.weight_numel,
+                index_node_limit=int(op.index_node_limit), index_edge_limit=int(op.index_edge_limit),
                 forward=dict(file=fwd_file, module=fwd_module, output_needs_zero=bool(op.forward_output_needs_zero),
                              degree_tiers=bool(op.forward_degree_tiers)),
                 backward=dict(file=bwd_file, module=bwd_module, segmented=bool(segmented), partials=int(partials),

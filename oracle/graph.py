@@ -1,6 +1,6 @@
 """CPU oracle for the graph tables of the convolution. TEST INFRASTRUCTURE ONLY.
 
-Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs may import this module.
+Test infrastructure: only the tests, the repository's smoke check and the benchmark's CPU-baseline legs may import this module.
 
 Restates, in numpy, the CPU branch of the reference's ``make_graph`` (``src/lunatp/graph.py:49-141``) and
 ``make_source_segments`` (``src/lunatp/uvu_conv/graph.py:38-99``): validation messages, destination CSR, source

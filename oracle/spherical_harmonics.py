@@ -1,6 +1,6 @@
 """CPU oracle for real spherical harmonics in the e3nn convention. TEST INFRASTRUCTURE ONLY.
 
-Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs may import this module.
+Test infrastructure: only the tests, the repository's smoke check and the benchmark's CPU-baseline legs may import this module.
 
 Restates the reference's own CPU evaluation ``polynomial_forward``
 (``src/o3/spherical_harmonics/replay.py:112-120``) of the Cartesian recurrence listed in

@@ -1,6 +1,6 @@
 """CPU oracle for the UVU tensor-product convolution. TEST INFRASTRUCTURE ONLY.
 
-Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs may import this module; the
+Test infrastructure: only the tests, the repository's smoke check and the benchmark's CPU-baseline legs may import this module; the
 product package never does.
 
 The reference (HPC-AI-Team/LunaEquivariance v0.3.0) has no CPU implementation of the convolution: its operator

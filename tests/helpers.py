@@ -74,3 +74,57 @@ def assert_close(actual, expected, dtype, what=""):
     error = (actual - expected).abs().max().item() if expected.numel() else 0.0
     assert error <= tolerance(dtype) * scale + 1e-300, f"{what}: max error {error:.3e} vs scale {scale:.3e}"
     return error / scale
+
+
+class EdgeSample:
+    """A subset of a large graph's edges as a small self-contained problem for the CPU oracle.
+
+    The sampled edges keep their order; the source rows and destination rows they touch are renumbered compactly.
+    ``take_*`` pull the matching rows of full-size device tensors to the CPU in float64.
+    """
+
+    def __init__(self, src, dst, edge_ids):
+        self.edge_ids = edge_ids
+        s, d = src[edge_ids].long(), dst[edge_ids].long()
+        self.src_nodes, self.src = torch.unique(s, return_inverse=True)
+        self.dst_nodes, self.dst = torch.unique(d, return_inverse=True)
+
+    @staticmethod
+    def _cpu(t):
+        return t.detach().to("cpu", torch.float64)
+
+    def take_edges(self, t):
+        return self._cpu(t[self.edge_ids])
+
+    def take_sources(self, t):
+        return self._cpu(t[self.src_nodes])
+
+    def take_destinations(self, t):
+        return self._cpu(t[self.dst_nodes])
+
+    @property
+    def cpu_src(self):
+        return self.src.cpu()
+
+    @property
+    def cpu_dst(self):
+        return self.dst.cpu()
+
+
+def in_edges_of(dst_rowptr, nodes):
+    """Edge ids (ascending) of all edges into the given destination nodes."""
+    begin, end = dst_rowptr[nodes].long(), dst_rowptr[nodes + 1].long()
+    return torch.cat([torch.arange(int(b), int(e), device=dst_rowptr.device) for b, e in zip(begin, end)])
+
+
+def out_edges_of(src_rowptr, edge_ids_by_src, nodes):
+    """Edge ids of all edges out of the given source nodes."""
+    begin, end = src_rowptr[nodes].long(), src_rowptr[nodes + 1].long()
+    return torch.cat([edge_ids_by_src[int(b):int(e)].long() for b, e in zip(begin, end)])
+
+
+def assert_rows_close(actual_rows, expected_rows, scale, dtype, what):
+    """``max|a - r| <= tol * scale`` where ``scale`` is the largest magnitude of the whole tensor."""
+    error = (actual_rows.detach().to("cpu", torch.float64) - expected_rows).abs().max().item()
+    assert error <= tolerance(dtype) * scale, f"{what}: max error {error:.3e} vs scale {scale:.3e}"
+    return error / scale

@@ -31,16 +31,19 @@ def test_sh_matches_reference_vectors_fp64(normalize, normalization, golden_npz)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
-@pytest.mark.parametrize("lmax", [1, 2, 3, 6])
-def test_sh_matches_oracle_on_unit_vectors(lmax, dtype):
+@pytest.mark.parametrize("normalize,normalization", [(True, "component"), (False, "integral"), (True, "norm")])
+@pytest.mark.parametrize("lmax", [1, 2, 3, 4, 5, 6, 7])
+def test_sh_degrees_zero_to_lmax_match_oracle(lmax, normalize, normalization, dtype):
+    """Degree lists 0..lmax: up to lmax 6 these take the kernels unrolled per lmax, 7 the run-time recurrence."""
     generator = torch.Generator().manual_seed(lmax)
-    v = torch.nn.functional.normalize(torch.randn(1000, 3, generator=generator, dtype=torch.float64), dim=-1)
+    v = torch.randn(1000, 3, generator=generator, dtype=torch.float64)
+    v = torch.nn.functional.normalize(v, dim=-1) * (1.0 if normalize else 0.7)
     C = (lmax + 1) ** 2
     g = torch.randn(1000, C, generator=generator, dtype=torch.float64)
     rx = torch.randn(1000, 3, generator=generator, dtype=torch.float64)
-    ref = oracle_sh.derivatives(tuple(range(lmax + 1)), v, True, "component", g, rx)
-    module = luna.o3.SphericalHarmonics(luna.Irreps.spherical_harmonics(lmax), normalize=True,
-                                        normalization="component")
+    ref = oracle_sh.derivatives(tuple(range(lmax + 1)), v, normalize, normalization, g, rx)
+    module = luna.o3.SphericalHarmonics(luna.Irreps.spherical_harmonics(lmax), normalize=normalize,
+                                        normalization=normalization)
     vd = v.to(DEVICE, dtype).requires_grad_(True)
     gd = g.to(DEVICE, dtype).requires_grad_(True)
     out = module(vd)

@@ -1,7 +1,8 @@
-"""Destination-range sharding on two CPU ranks (gloo): gathered sources, reduce-scattered gradients, uneven shards.
+"""Destination-range sharding on CPU ranks (gloo): halo exchange of source rows, return of their gradients, uneven
+shards.
 
 The convolution itself needs a GPU, so the CPU oracle stands in for it here; what is under test is the partition,
-the index renumbering and the two collectives with their autograd wiring.
+the renumbering into [owned rows | halo rows], the two all-to-all exchanges and their autograd wiring.
 """
 
 import os
@@ -40,11 +41,16 @@ def _worker(rank, world, port, results):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         meta, nodes, src, dst, x, y, w, g, rx = _problem()
-        counts = (9, 14)  # uneven on purpose
+        counts = COUNTS[world]  # uneven on purpose
         begin = sum(counts[:rank])
         mine = (dst >= begin) & (dst < begin + counts[rank])
         shard = sharded.make_graph_shard(src[mine], dst[mine], counts, rank)
-        assert shard.graph.num_nodes == counts[rank] and shard.graph.source_rows == 2 * 14
+        remote = src[mine][(src[mine] < begin) | (src[mine] >= begin + counts[rank])]
+        assert shard.halo_ids.tolist() == sorted(set(remote.tolist()))
+        assert shard.graph.num_nodes == counts[rank]
+        assert shard.graph.source_rows == counts[rank] + shard.halo_rows
+        assert sum(shard.recv_counts) == shard.halo_rows and shard.send_rows.numel() == sum(shard.send_counts)
+        assert shard.recv_counts[rank] == 0 and shard.send_counts[rank] == 0
         x_local = x[begin:begin + counts[rank]].clone().requires_grad_(True)
         w_local = w[mine].clone().requires_grad_(True)
 
@@ -60,8 +66,11 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-def test_two_rank_sharding_matches_single_rank():
-    world = 2
+COUNTS = {2: (9, 14), 3: (9, 3, 11)}
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharding_matches_single_rank(world):
     manager = mp.Manager()
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
@@ -77,10 +86,13 @@ def test_two_rank_sharding_matches_single_rank():
         torch.testing.assert_close(results[r][3], ref["hw"][mine], atol=1e-12, rtol=1e-12)
 
 
-def test_padded_source_index_and_ranges():
-    counts = (3, 5, 2)
-    index = sharded.padded_source_index(torch.tensor([0, 2, 3, 7, 8, 9]), counts, 5)
-    assert index.tolist() == [0, 2, 5, 9, 10, 11]
+def test_single_shard_without_exchange_and_ranges():
+    # one rank of a partition built without its peers: the halo ids say which rows to append by hand
+    src, dst = torch.tensor([0, 7, 4, 9, 3, 9]), torch.tensor([3, 3, 4, 4, 5, 5])
+    shard = sharded.make_graph_shard(src, dst, (3, 3, 4), 1, exchange=False)
+    assert shard.halo_ids.tolist() == [0, 7, 9] and shard.recv_counts == (1, 0, 2) and shard.send_counts == (0, 0, 0)
+    assert shard.graph.src.tolist() == [3, 4, 1, 5, 0, 5] and shard.graph.dst.tolist() == [0, 0, 1, 1, 2, 2]
+    assert shard.graph.source_rows == 6
     rowptr = torch.tensor([0, 10, 10, 30, 35, 60, 100])
     ranges = sharded.balanced_node_ranges(rowptr, 2)
     assert ranges[0][0] == 0 and ranges[-1][1] == 6 and ranges[0][1] == ranges[1][0]

@@ -55,15 +55,25 @@ def test_noalloc_backward_matches_regular_entry_point_twice():
     lib = _native.library()
     limit = lib.luna_uvu_conv_noalloc_max_scratch_bytes()
     assert limit == 8 << 20
+    with torch.cuda.device(DEVICE):
+        _native.check(lib.luna_uvu_conv_noalloc_prepare(op._plan.handle))  # set-up: the one step that may allocate
     # two different graphs back to back: the second call finds the first call's partial rows in the array
     for seed, (nodes, edges) in enumerate(((41, 333), (57, 1201))):
         graph, (x, y, w, g) = problem(conv, nodes, edges, dtype, seed)
         need = lib.luna_uvu_conv_scratch_bytes(op._plan.handle, nodes, edges)
         assert 0 < need <= limit, "the case must exercise the scratch path"
         want = conv_mod.run_backward(op, x, y, w, g, graph)  # regular entry point, torch-allocated scratch
-        status, got = call_noalloc(op, graph, x, y, w, g)
-        _native.check(status)
+        gx, gy, gw = torch.empty_like(x), torch.empty_like(y), torch.empty_like(w)  # outputs exist before the call
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        with torch.cuda.device(x.device):
+            status = lib.luna_uvu_conv_bwd_noalloc(
+                op._plan.handle, ctypes.byref(graph.native()), x.data_ptr(), y.data_ptr(), w.data_ptr(),
+                g.data_ptr(), gx.data_ptr(), gy.data_ptr(), gw.data_ptr(), _native.current_stream(x.device))
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+        _native.check(status)
+        got = (gx, gy, gw)
         for name, a, b in zip(("gx", "gy", "gw"), got, want):
             assert_close(a, b.detach().cpu(), dtype, f"noalloc {name} (call {seed + 1})")
     _native.check(lib.luna_uvu_check_status(op._plan.handle, None))
@@ -85,13 +95,26 @@ def test_noalloc_refuses_instead_of_allocating():
     status, _ = call_noalloc(op, graph, x, y, w, g)
     assert status == _native.LUNA_ERR_SCRATCH
     assert "8388608" in _native.last_error()
+    # without the edge-attribute gradient no scratch is used, so the same large graph is accepted
+    with torch.cuda.device(DEVICE):
+        _native.check(lib.luna_uvu_conv_noalloc_prepare(op._plan.handle))
+    want_x, _, want_w = conv_mod.run_backward(op, x, y, w, g, graph, needs=(True, False, True))
+    gx, gw = torch.empty_like(x), torch.empty_like(w)
+    with torch.cuda.device(x.device):
+        _native.check(lib.luna_uvu_conv_bwd_noalloc(
+            op._plan.handle, ctypes.byref(graph.native()), x.data_ptr(), y.data_ptr(), w.data_ptr(), g.data_ptr(),
+            gx.data_ptr(), None, gw.data_ptr(), _native.current_stream(x.device)))
+    torch.cuda.synchronize()
+    assert_close(gx, want_x.cpu(), dtype, "noalloc gx without gy")
+    assert_close(gw, want_w.cpu(), dtype, "noalloc gw without gy")
 
     fresh = make_conv("wide", dtype)  # its tables have never been uploaded to this device
     small_graph, (x, y, w, g) = problem(fresh, 33, 200, dtype, 8)
     status, _ = call_noalloc(fresh.op, small_graph, x, y, w, g)
     assert status == _native.LUNA_ERR_INVALID_ARGUMENT
-    assert "not on this device" in _native.last_error()
-    _native.check(lib.luna_uvu_check_status(fresh.op._plan.handle, None))  # uploads the tables
+    assert "luna_uvu_conv_noalloc_prepare" in _native.last_error()
+    with torch.cuda.device(DEVICE):
+        _native.check(lib.luna_uvu_conv_noalloc_prepare(fresh.op._plan.handle))
     want = conv_mod.run_backward(fresh.op, x, y, w, g, small_graph)
     status, got = call_noalloc(fresh.op, small_graph, x, y, w, g)
     _native.check(status)
