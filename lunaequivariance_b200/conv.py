@@ -9,7 +9,19 @@ Mirrors the reference's layers for this path:
   (shape) implementations and ``register_autograd`` chain - ``src/lunatp/uvu_conv/interface.py:18-140``.
 
 All arithmetic happens in the C-ABI library; missing cotangents are passed as null pointers and never
-materialised.  Third-order derivatives, the per-edge envelope ``env`` and ``return_l0_feat`` are not provided.
+materialised.
+
+Beyond the fused first- and second-order kernels, three features of the reference are composed from the same
+kernels rather than given kernels of their own:
+
+* ``env`` (per-edge envelope, ``src/lunatp/uvu_conv/kernels/forward.py:141-148``): the message of an edge is linear in
+  the edge attributes, so scaling the message by ``env[e]`` is scaling ``edge_attr[e]`` (16 numbers instead of a
+  weight row); the product is a torch op and autograd supplies the envelope's gradients at every order;
+* ``return_l0_feat`` (per-edge scalar outputs, layout of ``src/lunatp/utils/layout.py:171-189``): the same operator
+  restricted to the paths into degree 0, run on the graph in which every edge is its own destination;
+* third and higher derivatives (``kernels/triple_backward.py``): every derivative of the four-linear form
+  ``F(x, y, w, g)`` is again a partial derivative of ``F`` with other operands, so one autograd function
+  (``_Partial``) that maps each free slot onto the forward or the backward kernel is closed under differentiation.
 """
 
 from __future__ import annotations
@@ -23,7 +35,7 @@ import numpy as np
 import torch
 
 from . import _native
-from .graph import LunaTPGraph
+from .graph import LunaTPGraph, make_graph
 from .paths import TensorProductPaths, build_uvu_conv_metadata
 
 _DTYPE_NAMES = {torch.float32: "float32", torch.float64: "float64"}
@@ -109,7 +121,8 @@ class LunaTPUVUConv:
         self.weight_numel = int(meta["weight_numel"])
         self.max_channels = int(meta.get("max_channels", max(int(s["channels"]) for s in meta["generated_specs"])))
         self.generated_specs = list(meta["generated_specs"])
-        self.l0_dim = 0
+        self.l0_offsets, self.l0_dim = l0_feature_layout(self.generated_specs)
+        self._l0_operator = None
         self.lunatp_backend = "lunatp_uvuconv_fp64" if dtype == torch.float64 else "lunatp_uvuconv_fp32"
         self.lunatp_dtype = dtype
         self._plan = _Plan(self.meta, dtype)  # host-only; also validates the path list
@@ -127,10 +140,23 @@ class LunaTPUVUConv:
             ]
             self._torch_config = json.dumps(
                 dict(mode="uvu_conv", dtype=_DTYPE_NAMES[self.compute_dtype], index_bits=self.index_bits,
-                     out_dim=self.out_dim, l0_dim=0, weight_mode="external", meta=meta),
+                     out_dim=self.out_dim, l0_dim=self.l0_dim, weight_mode="external", meta=meta),
                 separators=(",", ":"),
             )
         return self._torch_config
+
+    @property
+    def l0_operator(self) -> "LunaTPUVUConv | None":
+        """The operator whose output rows are the per-edge scalar features: this operator's paths into degree 0,
+        each instruction writing its own block of ``channels`` columns (``None`` if there is no such path)."""
+        if self.l0_dim == 0:
+            return None
+        if self._l0_operator is None:
+            specs = [dict(spec, out_offset=self.l0_offsets[index])
+                     for index, spec in enumerate(self.generated_specs) if index in self.l0_offsets]
+            meta = dict(self.meta, out_dim=self.l0_dim, generated_specs=specs)
+            self._l0_operator = LunaTPUVUConv(meta, dtype=self.compute_dtype, index_bits=self.index_bits)
+        return self._l0_operator
 
     @property
     def uses_staged_kernels(self) -> bool:
@@ -176,6 +202,36 @@ class LunaTPUVUConv:
     @staticmethod
     def run(op, x, edge_attr, weight, *, graph, env=None, return_l0_feat=False):
         return lunatp_uvu_conv_func(op, x, edge_attr, weight, graph=graph, env=env, return_l0_feat=return_l0_feat)
+
+
+def l0_feature_layout(specs) -> tuple[dict, int]:
+    """Column offset of every path into degree 0 and the total width of the per-edge scalar features.
+
+    Blocks follow the order of the paths' output offsets; the specs one instruction was split into (several channels
+    of the second input) share the instruction's block.
+    """
+    offsets, blocks, width = {}, {}, 0
+    for index, spec in sorted(enumerate(specs), key=lambda item: int(item[1]["out_offset"])):
+        if int(spec["l3"]) != 0:
+            continue
+        block = ("instruction", int(spec["l0_path"])) if "l0_path" in spec else ("path", index)
+        if block not in blocks:
+            blocks[block] = width
+            width += int(spec["channels"])
+        offsets[index] = blocks[block]
+    return offsets, width
+
+
+def edge_output_graph(graph: LunaTPGraph) -> LunaTPGraph:
+    """The graph with the same sources in which edge ``e`` is destination ``e``: a convolution on it returns the
+    messages themselves, one row per edge.  Built once per graph and kept with it."""
+    cached = graph._tables.get("edge_output_graph")
+    if cached is None:
+        edges = graph.num_edges
+        own = torch.arange(edges, device=graph.src.device, dtype=torch.int32)
+        cached = make_graph(graph.src, own, edges, num_src_nodes=graph.source_rows)
+        graph._tables["edge_output_graph"] = cached
+    return cached
 
 
 def create_uvu_conv_operator(official_tp_or_meta, *, dtype=None) -> LunaTPUVUConv:
@@ -416,17 +472,85 @@ class UVUConvBackward(torch.autograd.Function):
         return (None, hx, hy, hw, hg, None, None)
 
 
+class _Partial(torch.autograd.Function):
+    """``dF/d(slot)`` of the four-linear form ``F(x, y, w, g)`` at the other three operands (slot 0..3 = x, y, w, g).
+
+    The operand passed in the free slot only lends its shape.  ``<r, dF/ds(a, b, c)> = F(s=r, a, b, c)``, so the
+    gradient with respect to operand ``a`` is ``dF/da`` with the cotangent ``r`` in slot ``s``: the backward of this
+    function is this function again, which makes derivatives of any order available.
+    """
+
+    @staticmethod
+    def forward(ctx, op, graph, slot, x, y, w, g):
+        ctx.op, ctx.graph, ctx.slot = op, graph, slot
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(x, y, w, g)
+        if slot == 3:
+            return run_forward(op, x, y, w, graph)
+        return run_backward(op, x, y, w, g, graph, needs=tuple(i == slot for i in range(3)))[slot]
+
+    @staticmethod
+    def backward(ctx, r):
+        grads = [None] * 4
+        if r is not None:
+            operands = list(ctx.saved_tensors)
+            operands[ctx.slot] = r.contiguous()
+            for other in range(4):
+                if other != ctx.slot and ctx.needs_input_grad[3 + other]:
+                    grads[other] = _Partial.apply(ctx.op, ctx.graph, other, *operands)
+        return (None, None, None, *grads)
+
+
+def run_triple_backward(op, x, y, w, g, rx, ry, rw, bx, by, bw, bg, graph, needs=(True,) * 7):
+    """Gradients of ``<bx,hx> + <by,hy> + <bw,hw> + <bg,hg>`` (the second-order outputs contracted with their
+    cotangents) with respect to ``x, y, w, g, rx, ry, rw``; missing cotangents and tangents are skipped."""
+    leaves = [None if t is None else t.detach().requires_grad_(bool(need))
+              for t, need in zip((x, y, w, g, rx, ry, rw), needs)]
+    X, Y, W, G, RX, RY, RW = leaves
+    with torch.enable_grad():
+        def partial(slot, a, b, c, d):
+            return _Partial.apply(op, graph, slot, a, b, c, d)
+
+        # second-order outputs as sums of partials (src/lunatp/utils/contractions.py:41-49)
+        programs = (
+            (bx, 0, ((X, RY, W, G), (X, Y, RW, G))),
+            (by, 1, ((RX, Y, W, G), (X, Y, RW, G))),
+            (bw, 2, ((RX, Y, W, G), (X, RY, W, G))),
+            (bg, 3, ((RX, Y, W, G), (X, RY, W, G), (X, Y, RW, G))),
+        )
+        outputs, seeds = [], []
+        for seed, slot, terms in programs:
+            if seed is None:
+                continue
+            parts = [partial(slot, *operands) for operands in terms if all(o is not None for o in operands)]
+            if parts:
+                outputs.append(sum(parts[1:], parts[0]))
+                seeds.append(seed.contiguous())
+        wanted = [leaf for leaf, need in zip(leaves, needs) if leaf is not None and need]
+        found = iter(torch.autograd.grad(outputs, wanted, seeds, allow_unused=True)) if outputs and wanted else iter(())
+    result = []
+    for leaf, need in zip(leaves, needs):
+        value = next(found, None) if (leaf is not None and need) else None
+        result.append(value)
+    return tuple(result)
+
+
 class UVUConvDoubleBackward(torch.autograd.Function):
     @staticmethod
     def forward(ctx, op, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True)):
+        ctx.op, ctx.graph = op, graph
         ctx.set_materialize_grads(False)
+        ctx.save_for_backward(x, y, w, g, rx, ry, rw)
         return run_double_backward(op, x, y, w, g, rx, ry, rw, graph, needs=tuple(needs))
 
     @staticmethod
-    def backward(ctx, *grads):
-        if all(g is None for g in grads):
+    def backward(ctx, bx, by, bw, bg):
+        if bx is None and by is None and bw is None and bg is None:
             return (None,) * 10
-        raise NotImplementedError("third-order derivatives of the UVU convolution are not provided")
+        x, y, w, g, rx, ry, rw = ctx.saved_tensors
+        needs = _engine_needs(ctx.needs_input_grad[1:8])
+        grads = run_triple_backward(ctx.op, x, y, w, g, rx, ry, rw, bx, by, bw, bg, ctx.graph, needs=needs)
+        return (None, *grads, None, None)
 
 
 # ----------------------------------------------------------------------------------------------- custom ops
@@ -438,7 +562,9 @@ class UVUConvDoubleBackward(torch.autograd.Function):
            "str config) -> (Tensor, Tensor?)")
 def conv_forward(x, y, w, env, tables, num_nodes, return_l0, config):
     if env is not None or return_l0:
-        raise NotImplementedError("env and return_l0_feat are not provided")
+        # this library composes both outside the op (see lunatp_uvu_conv_func): the envelope as a product with the
+        # edge attributes, the per-edge scalar features as a second call of this op
+        raise NotImplementedError("pass env and return_l0_feat to the module or to lunatp_uvu_conv_func")
     op = compiled_operator(config)
     return run_forward(op, x, y, w, _GraphView(tables, num_nodes)), None
 
@@ -483,6 +609,29 @@ def _(x, y, w, env, g, gl0, rx, ry, rw, re, tables, num_nodes, needs, config):
                  for v, need in zip((x, y, w, env, g, gl0), needs))
 
 
+@torch.library.custom_op(
+    "lunatp::uvu_conv_triple_backward", mutates_args=(),
+    schema="(Tensor x, Tensor y, Tensor w, Tensor? env, Tensor g, Tensor? gl0, Tensor? rx, Tensor? ry, Tensor? rw, "
+           "Tensor? re, Tensor? sx, Tensor? sy, Tensor? sw, Tensor? sg, Tensor? se, Tensor? sl0, Tensor?[] tables, "
+           "SymInt num_nodes, bool[] needs, str config) -> (Tensor?, Tensor?, Tensor?, Tensor?, Tensor?, Tensor?, "
+           "Tensor?, Tensor?, Tensor?, Tensor?)")
+def conv_triple_backward(x, y, w, env, g, gl0, rx, ry, rw, re, sx, sy, sw, sg, se, sl0, tables, num_nodes, needs,
+                         config):
+    """Outputs in the reference's order (dx, dy, dw, de, dg, dl0, drx, dry, drw, dre); the envelope and scalar-feature
+    slots are always None here."""
+    op = compiled_operator(config)
+    want = (needs[0], needs[1], needs[2], needs[4], needs[6], needs[7], needs[8])
+    dx, dy, dw, dg, drx, dry, drw = run_triple_backward(op, x, y, w, g, rx, ry, rw, sx, sy, sw, sg,
+                                                        _GraphView(tables, num_nodes), needs=want)
+    return dx, dy, dw, None, dg, None, drx, dry, drw, None
+
+
+@conv_triple_backward.register_fake
+def _(x, y, w, env, g, gl0, rx, ry, rw, re, sx, sy, sw, sg, se, sl0, tables, num_nodes, needs, config):
+    return tuple(torch.empty_like(v, memory_format=torch.contiguous_format) if need and v is not None else None
+                 for v, need in zip((x, y, w, env, g, gl0, rx, ry, rw, re), needs))
+
+
 def _setup_forward(ctx, inputs, output):
     x, y, w, env, tables, ctx.num_nodes, _, ctx.config = inputs
     ctx.save_for_backward(x, y, w, *tables)
@@ -519,26 +668,34 @@ def _backward_backward(ctx, rx, ry, rw, re):
     return hx, hy, hw, None, hg, None, table_grad, None, None, None
 
 
+def _setup_double_backward(ctx, inputs, output):
+    x, y, w, env, g, gl0, rx, ry, rw, re, tables, ctx.num_nodes, _, ctx.config = inputs
+    ctx.save_for_backward(x, y, w, g, rx, ry, rw, *tables)
+    ctx.table_count = len(tables)
+    ctx.set_materialize_grads(False)
+
+
+def _double_backward_backward(ctx, sx, sy, sw, se, sg, sl0):
+    x, y, w, g, rx, ry, rw, *tables = ctx.saved_tensors
+    table_grad = [None] * ctx.table_count
+    if sx is None and sy is None and sw is None and sg is None:
+        return (None,) * 10 + (table_grad, None, None, None)
+    needs = [bool(n) for n in ctx.needs_input_grad[:10]]
+    needs[3] = needs[5] = needs[9] = False  # envelope and scalar-feature slots
+    dx, dy, dw, _, dg, _, drx, dry, drw, _ = conv_triple_backward(
+        x, y, w, None, g, None, rx, ry, rw, None, sx, sy, sw, sg, None, None, tables, ctx.num_nodes, needs, ctx.config)
+    return dx, dy, dw, None, dg, None, drx, dry, drw, None, table_grad, None, None, None
+
+
 conv_forward.register_autograd(_forward_backward, setup_context=_setup_forward)
 conv_backward.register_autograd(_backward_backward, setup_context=_setup_backward)
+conv_double_backward.register_autograd(_double_backward_backward, setup_context=_setup_double_backward)
 
 
 # ----------------------------------------------------------------------------------------------- functional entry
 
 
-def lunatp_uvu_conv_func(op: LunaTPUVUConv, x, edge_attr, weight, *, graph: LunaTPGraph, env=None,
-                         return_l0_feat: bool = False):
-    """Aggregate UVU edge messages by destination, differentiable to second order.
-
-    ``x`` [num_nodes, in1_dim], ``edge_attr`` [num_edges, in2_dim], ``weight`` [num_edges, weight_numel] share one
-    CUDA device and the operator's dtype; edge data follows the order of the graph's edge list.
-    """
-    if env is not None or return_l0_feat:
-        raise NotImplementedError("env and return_l0_feat are not provided by this build")
-    if weight is None:
-        raise TypeError("UVU convolution requires explicit per-edge weights")
-    if not isinstance(graph, LunaTPGraph):
-        raise TypeError("graph must be a LunaTPGraph prepared with make_graph / create_graph")
+def _conv(op: LunaTPUVUConv, x, edge_attr, weight, graph: LunaTPGraph):
     if is_compiling():
         out, _ = torch.ops.lunatp.uvu_conv_forward.default(
             x.contiguous(), edge_attr.contiguous(), weight.contiguous(), None, graph.table_list(),
@@ -547,5 +704,38 @@ def lunatp_uvu_conv_func(op: LunaTPUVUConv, x, edge_attr, weight, *, graph: Luna
     return UVUConvForward.apply(op, _through_view(x), _through_view(edge_attr), _through_view(weight), graph)
 
 
+def lunatp_uvu_conv_func(op: LunaTPUVUConv, x, edge_attr, weight, *, graph: LunaTPGraph, env=None,
+                         return_l0_feat: bool = False):
+    """Aggregate UVU edge messages by destination, differentiable to any order.
+
+    ``x`` [num_nodes, in1_dim], ``edge_attr`` [num_edges, in2_dim], ``weight`` [num_edges, weight_numel] share one
+    CUDA device and the operator's dtype; edge data follows the order of the graph's edge list.  ``env``
+    ([num_edges] or [num_edges, 1]) scales each edge's message before aggregation.  With ``return_l0_feat`` the result
+    is ``(out, l0_feat)``: ``l0_feat`` [num_edges, l0_dim] holds the raw per-edge contributions of the paths into
+    degree 0 (one column per channel of each such instruction), without ``env``.
+    """
+    if weight is None:
+        raise TypeError("UVU convolution requires explicit per-edge weights")
+    if not isinstance(graph, LunaTPGraph):
+        raise TypeError("graph must be a LunaTPGraph prepared with make_graph / create_graph")
+    scaled = edge_attr
+    if env is not None:
+        if env.ndim == 1:
+            env = env.unsqueeze(-1)
+        if env.ndim != 2 or env.shape[0] != edge_attr.shape[0] or env.shape[1] != 1:
+            raise ValueError(f"env must have shape ({edge_attr.shape[0]},) or ({edge_attr.shape[0]}, 1), "
+                             f"got {tuple(env.shape)}")
+        if env.dtype != edge_attr.dtype or env.device != edge_attr.device:
+            raise TypeError("env must share the dtype and device of edge_attr")
+        scaled = edge_attr * env  # the message is linear in the edge attributes
+    out = _conv(op, x, scaled, weight, graph)
+    if not return_l0_feat:
+        return out
+    scalar_op = op.l0_operator
+    if scalar_op is None or graph.num_edges == 0:
+        return out, edge_attr.new_zeros((graph.num_edges, op.l0_dim))
+    return out, _conv(scalar_op, x, edge_attr, weight, edge_output_graph(graph))
+
+
 __all__ = ["LunaTPUVUConv", "create_uvu_conv_operator", "lunatp_uvu_conv_func", "run_forward", "run_backward",
-           "run_double_backward", "UVUConvForward", "UVUConvBackward", "UVUConvDoubleBackward"]
+           "run_double_backward", "run_triple_backward", "l0_feature_layout", "edge_output_graph", "UVUConvForward", "UVUConvBackward", "UVUConvDoubleBackward"]

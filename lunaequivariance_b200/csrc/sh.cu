@@ -399,23 +399,6 @@ struct CanonForwardSink {
   }
 };
 template <typename T>
-struct CanonBackwardSink {
-  int normalization;
-  const T* row;
-  T dx = T(0), dy = T(0), dz = T(0);
-  template <int L>
-  __device__ __forceinline__ void emit(std::integral_constant<int, L>, const G3<T>* level) {
-    const T scale = degree_scale<T>(L, normalization);
-#pragma unroll
-    for (int m = 0; m < 2 * L + 1; ++m) {
-      const T gsum = scale * row[L * L + m];
-      dx += gsum * level[m].x;
-      dy += gsum * level[m].y;
-      dz += gsum * level[m].z;
-    }
-  }
-};
-template <typename T>
 struct CanonDoubleSink {
   int normalization;
   T* row;  // g row on entry; overwritten with sg
@@ -434,6 +417,94 @@ struct CanonDoubleSink {
     }
   }
 };
+
+// First derivative for the degree list 0..LMAX in reverse mode: dv = J^T g.  The forward sweep keeps every level's
+// values in registers; the reverse sweep walks the recurrence from the highest degree down, handing each component's
+// adjoint to the components it was computed from and to the coordinates.  About 12 operations per output component,
+// against about 30 for carrying a gradient along the forward recurrence, and no wider state than the values
+// themselves.  All indices are compile-time constants.
+template <typename T, int LMAX>
+__device__ __forceinline__ void canon_backward(const ShParams& P, T vx, T vy, T vz, const T* __restrict__ grow,
+                                               T& dvx, T& dvy, T& dvz) {
+  constexpr int C = (LMAX + 1) * (LMAX + 1);
+  // coordinates the polynomials are evaluated at
+  T x = vx, y = vy, z = vz, inv = T(1);
+  bool unit = false;
+  if (P.normalize) {
+    const T len2 = vx * vx + vy * vy + vz * vz;
+    unit = len2 > T(1e-24);
+    inv = unit ? T(1) / sqrt(len2) : T(1e12);
+    x *= inv;
+    y *= inv;
+    z *= inv;
+  }
+  const T r2 = x * x + y * y + z * z;
+  T val[C], adj[C];
+  val[0] = T(1);
+  if constexpr (LMAX >= 1) {
+    val[1] = T(coef_diag(1)) * x;
+    val[2] = T(coef_diag(1)) * y;
+    val[3] = T(coef_diag(1)) * z;
+  }
+  unroll<2, LMAX + 1>([&](auto lc) {
+    constexpr int l = decltype(lc)::value;
+    constexpr int o = l * l, o1 = (l - 1) * (l - 1), o2 = (l - 2) * (l - 2);
+    constexpr T edge = T(coef_edge(l)), diag = T(coef_diag(l));
+    val[o] = edge * (val[o1] * z + val[o1 + 2 * l - 2] * x);
+    val[o + 2 * l] = edge * (val[o1 + 2 * l - 2] * z - val[o1] * x);
+    val[o + 1] = diag * y * val[o1];
+    val[o + 2 * l - 1] = diag * y * val[o1 + 2 * l - 2];
+    unroll<2, 2 * l - 1>([&](auto mc) {
+      constexpr int m = decltype(mc)::value;
+      val[o + m] = T(coef_a(l, m)) * y * val[o1 + m - 1] - T(coef_b(l, m)) * r2 * val[o2 + m - 2];
+    });
+  });
+  // seeds: the cotangent of every output component, with the degree's normalisation factor
+  unroll<0, LMAX + 1>([&](auto lc) {
+    constexpr int l = decltype(lc)::value;
+    const T scale = degree_scale<T>(l, P.normalization);
+#pragma unroll
+    for (int m = 0; m < 2 * l + 1; ++m) adj[l * l + m] = scale * grow[l * l + m];
+  });
+  T ax = T(0), ay = T(0), az = T(0), ar2 = T(0);
+  unroll<0, LMAX - 1>([&](auto dc) {
+    constexpr int l = LMAX - decltype(dc)::value;  // LMAX ... 2
+    constexpr int o = l * l, o1 = (l - 1) * (l - 1), o2 = (l - 2) * (l - 2);
+    constexpr T edge = T(coef_edge(l)), diag = T(coef_diag(l));
+    unroll<2, 2 * l - 1>([&](auto mc) {
+      constexpr int m = decltype(mc)::value;
+      const T ma = adj[o + m] * T(coef_a(l, m)), mb = adj[o + m] * T(coef_b(l, m));
+      ay += ma * val[o1 + m - 1];
+      adj[o1 + m - 1] += ma * y;
+      ar2 -= mb * val[o2 + m - 2];
+      adj[o2 + m - 2] -= mb * r2;
+    });
+    const T a0 = adj[o] * edge, a2l = adj[o + 2 * l] * edge, a1 = adj[o + 1] * diag, a2l1 = adj[o + 2 * l - 1] * diag;
+    adj[o1] += a0 * z - a2l * x + a1 * y;
+    adj[o1 + 2 * l - 2] += a0 * x + a2l * z + a2l1 * y;
+    az += a0 * val[o1] + a2l * val[o1 + 2 * l - 2];
+    ax += a0 * val[o1 + 2 * l - 2] - a2l * val[o1];
+    ay += a1 * val[o1] + a2l1 * val[o1 + 2 * l - 2];
+  });
+  if constexpr (LMAX >= 1) {
+    ax += T(coef_diag(1)) * adj[1];
+    ay += T(coef_diag(1)) * adj[2];
+    az += T(coef_diag(1)) * adj[3];
+  }
+  ax += T(2) * x * ar2;
+  ay += T(2) * y * ar2;
+  az += T(2) * z * ar2;
+  if (unit) {  // u = v / |v|: dv = (du - u (u . du)) / |v|
+    const T along = x * ax + y * ay + z * az;
+    dvx = inv * (ax - x * along);
+    dvy = inv * (ay - y * along);
+    dvz = inv * (az - z * along);
+  } else {  // no normalisation, or the clamped divisor: a constant factor
+    dvx = inv * ax;
+    dvy = inv * ay;
+    dvz = inv * az;
+  }
+}
 
 // Same three modes as sh_kernel for the degree list 0..LMAX, everything about the list known at compile time.
 template <typename T, int MODE, int LMAX>
@@ -474,15 +545,12 @@ sh_canon_kernel(const ShParams P, const T* __restrict__ v, const T* __restrict__
 #pragma unroll 4
       for (int idx = lane; idx < rows * C; idx += 32) dst[idx] = tile[(idx / C) * CP + (idx % C)];
     } else if constexpr (MODE == 1) {
-      using N = G3<T>;
-      N x{vx, T(1), T(0), T(0)}, y{vy, T(0), T(1), T(0)}, z{vz, T(0), T(0), T(1)}, r2;
-      prepare<T, N>(P, x, y, z, r2);
-      CanonBackwardSink<T> sink{P.normalization, row};
-      walk_unrolled<T, N, LMAX>(N{T(1), T(0), T(0), T(0)}, x, y, z, r2, sink);
+      T dvx, dvy, dvz;
+      canon_backward<T, LMAX>(P, vx, vy, vz, row, dvx, dvy, dvz);
       if (active) {
-        out0[item * 3 + 0] = sink.dx;
-        out0[item * 3 + 1] = sink.dy;
-        out0[item * 3 + 2] = sink.dz;
+        out0[item * 3 + 0] = dvx;
+        out0[item * 3 + 1] = dvy;
+        out0[item * 3 + 2] = dvz;
       }
     } else {
       using N = Du<G3<T>>;

@@ -98,6 +98,107 @@ __device__ __forceinline__ void reduce_tile_rows(const T* red, T* out, int lane)
   __syncwarp();
 }
 
+// ---- one path of the sparse formulation, row by row ------------------------------------------------------------------
+// Positions inside a pattern's term list, which is sorted by (i, k, j): where the row of term t ends, and which
+// distinct (i, k) of its row a term belongs to.
+template <typename PT>
+__host__ __device__ constexpr int pattern_row_end(int t0) {
+  int t = t0;
+  while (t < PT::n && PT::t[t].i == PT::t[t0].i) ++t;
+  return t;
+}
+template <typename PT>
+__host__ __device__ constexpr int pattern_ik_slot(int t0, int t) {
+  int slot = 0;
+  for (int q = t0 + 1; q <= t; ++q)
+    if (PT::t[q].k != PT::t[q - 1].k) ++slot;
+  return slot;
+}
+
+// Computes one path for a lane's packets.  xl / gxl: the lane's x and gx packets of degree l1; g2: its g packets of
+// degree l3; w2: its weights; dot: receives sum_i x_i s_i (the weight gradient before unpacking).
+//
+// The arithmetic of a row i is issued in three batches of mutually independent instructions, so that the latency of
+// one is covered by the others even when few warps are resident:
+//   P_ik = sum over the lane's packets of (x_i w) g_k      for every distinct k of the row
+//   gy_j += c_t P_ik                                       for every term of the row
+//   s_i   = sum_t (c_t y_j) g_k                            in two alternating partial sums
+template <typename T, int CPL, int LX, int L2, int LO, int l1, int l2, int l3, bool WXW, bool WY, typename V>
+__device__ __forceinline__ void sparse_path_rows(const V* xl, V* gxl, V* gy2, const V* g2, const V* w2, V* dot,
+                                                 const T* cybuf, const T* ctab) {
+  using PK = PkT<T, CPL, UsePairs<T, CPL>::value>;
+  constexpr int NP = PK::NP;
+  using PT = CgPattern<l1, l2, l3>;
+  constexpr int n = PT::n;
+  constexpr int toff = canon_toff(LX, L2, LO, l1, l2, l3);
+#pragma unroll
+  for (int p = 0; p < NP; ++p) dot[p] = zero_packet<V>();
+  static_for<0, n>([&](auto tc) {
+    constexpr int t0 = decltype(tc)::value;
+    constexpr bool row_first = t0 == 0 || PT::t[t0 == 0 ? 0 : t0 - 1].i != PT::t[t0].i;
+    if constexpr (row_first) {
+      constexpr int i = PT::t[t0].i;
+      constexpr int t1 = pattern_row_end<PT>(t0);
+      constexpr int len = t1 - t0;
+      constexpr int g_lo = t0 / 4, g_hi = (t1 - 1) / 4;  // groups of four table entries that cover the row
+      T cy[WXW ? 4 * (g_hi - g_lo + 1) : 1], cc[WY ? 4 * (g_hi - g_lo + 1) : 1];
+      static_for<g_lo, g_hi + 1>([&](auto gc) {
+        constexpr int group = decltype(gc)::value;
+        if constexpr (WXW) load_four<T>(cybuf + toff + 4 * group, cy + 4 * (group - g_lo));
+        if constexpr (WY) load_four<T>(ctab + toff + 4 * group, cc + 4 * (group - g_lo));
+      });
+      if constexpr (WY) {
+        V xw[NP];
+#pragma unroll
+        for (int p = 0; p < NP; ++p) xw[p] = vmul(xl[i * NP + p], w2[p]);
+        constexpr int slots = pattern_ik_slot<PT>(t0, t1 - 1) + 1;
+        V pik[slots];
+        static_for<t0, t1>([&](auto uc) {
+          constexpr int t = decltype(uc)::value;
+          constexpr bool ik_first = t == t0 || PT::t[t - 1].k != PT::t[t].k;
+          if constexpr (ik_first) {
+            constexpr int k = PT::t[t].k, slot = pattern_ik_slot<PT>(t0, t);
+            pik[slot] = vmul(xw[0], g2[k * NP]);
+#pragma unroll
+            for (int p = 1; p < NP; ++p) pik[slot] = vfma(xw[p], g2[k * NP + p], pik[slot]);
+          }
+        });
+        static_for<t0, t1>([&](auto uc) {
+          constexpr int t = decltype(uc)::value;
+          constexpr int j = PT::t[t].j, slot = pattern_ik_slot<PT>(t0, t);
+          gy2[l2 * l2 + j] = vfma(bcast_packet(cc[t - 4 * g_lo], V{}), pik[slot], gy2[l2 * l2 + j]);
+        });
+      }
+      if constexpr (WXW) {
+        V sa[NP], sb[NP];
+        static_for<t0, t1>([&](auto uc) {
+          constexpr int t = decltype(uc)::value;
+          constexpr int k = PT::t[t].k, r = t - t0;
+          const V c = bcast_packet(cy[t - 4 * g_lo], V{});
+#pragma unroll
+          for (int p = 0; p < NP; ++p) {
+            if constexpr (r == 0) {
+              sa[p] = vmul(c, g2[k * NP + p]);
+            } else if constexpr (r == 1) {
+              sb[p] = vmul(c, g2[k * NP + p]);
+            } else if constexpr (r % 2 == 0) {
+              sa[p] = vfma(c, g2[k * NP + p], sa[p]);
+            } else {
+              sb[p] = vfma(c, g2[k * NP + p], sb[p]);
+            }
+          }
+        });
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+          if constexpr (len >= 2) sa[p] = vadd(sa[p], sb[p]);
+          gxl[i * NP + p] = vfma(w2[p], sa[p], gxl[i * NP + p]);
+          dot[p] = vfma(xl[i * NP + p], sa[p], dot[p]);
+        }
+      }
+    }
+  });
+}
+
 // Warps per CTA at most (caps the registers per thread): FP32 with at most two channels per lane needs fewer
 // registers and runs up to 12 warps (168 registers), everything else 8 (255).
 #ifndef LUNA_SPARSE_WARPS_SMALL
@@ -253,7 +354,11 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL, LX, L2, LO>() * 32, 1
     load_lane_packets<PK, T, CPL>(wq, w2);
     const V* xl = &xr[l1 * l1 * NP];
     V* gxl = &gxr[l1 * l1 * NP];
-    V dot[NP], sv[NP], xw[NP];
+    V dot[NP];
+#ifdef LUNA_PATH_ROWS
+    sparse_path_rows<T, CPL, LX, L2, LO, l1, l2, l3, WXW, WY, V>(xl, gxl, gy2, g2, w2, dot, cybuf, ctab);
+#else
+    V sv[NP], xw[NP];
     V pik = zero_packet<V>();
 #pragma unroll
     for (int p = 0; p < NP; ++p) dot[p] = sv[p] = xw[p] = zero_packet<V>();
@@ -297,6 +402,7 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL, LX, L2, LO>() * 32, 1
         }
       });
     });
+#endif
     if (want_w) {
       T gwv[CPL];
       unpack_packets<PK, T, CPL, 1>(dot, gwv);

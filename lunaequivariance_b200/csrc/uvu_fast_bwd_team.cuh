@@ -32,15 +32,15 @@ namespace luna {
 namespace fastk {
 
 constexpr int kTeamWarps = 2;      // warps that share an edge
-constexpr int kTeamStages = 2;     // weight-row stages per team
+constexpr int kTeamMaxStages = 4;  // weight-row stages per team (at most; the launcher picks 2..4)
 constexpr int kTeamMaxSlots = 4;   // slots of a team's g ring (at most)
 constexpr int kTeamMaxTeams = 6;   // teams per CTA: 12 warps, which caps the registers per thread at 168
-constexpr int kTeamSumBuffers = 3; // buffers for the two warps' gy sums (three: see the hand-off at the end of an edge)
+constexpr int kTeamSumBuffers = kTeamMaxStages + 1;  // buffers for the warps' gy sums (see the hand-off after an edge)
 
 // Barriers of one team (row landed, per stage; g block landed, per slot), then its counters as 32-bit words (warps
 // done with a stage, with a slot, with a gy sum buffer).
-constexpr int kTeamBarriers = kTeamStages + kTeamMaxSlots;
-constexpr int kTeamCounters = kTeamStages + kTeamMaxSlots + kTeamSumBuffers + 1;
+constexpr int kTeamBarriers = kTeamMaxStages + kTeamMaxSlots;
+constexpr int kTeamCounters = kTeamMaxStages + kTeamMaxSlots + kTeamSumBuffers + 1;
 
 // Shared memory of one warp: per-edge scalars c_t y_j, reduction tile, reduced gy row, y row.
 template <typename T>
@@ -50,9 +50,9 @@ __host__ __device__ inline size_t team_warp_elems(const FastMeta& f) {
 }
 // Shared memory of one team.
 template <typename T>
-__host__ __device__ inline size_t team_bytes(const FastMeta& f, int slots) {
+__host__ __device__ inline size_t team_bytes(const FastMeta& f, int stages, int slots) {
   const size_t gslot = static_cast<size_t>(f.ch) * (2 * f.LO + 1);
-  const size_t elems = static_cast<size_t>(kTeamStages) * f.W + static_cast<size_t>(slots) * gslot +
+  const size_t elems = static_cast<size_t>(stages) * f.W + static_cast<size_t>(slots) * gslot +
                        kTeamWarps * team_warp_elems<T>(f) + kTeamSumBuffers * kTeamWarps * 32;
   return (elems * sizeof(T) + kTeamBarriers * sizeof(uint64_t) + kTeamCounters * sizeof(unsigned) + 127) / 128 * 128;
 }
@@ -80,7 +80,11 @@ __device__ __forceinline__ void team_path(const V* xl, V* gxl, V* gy2, const V* 
   constexpr int toff = canon_toff(LX, L2, LO, l1, l2, l3);
   V w2[NP];
   load_lane_packets<PK, T, CPL>(wq, w2);
-  V dot[NP], sv[NP], xw[NP];
+  V dot[NP];
+#ifdef LUNA_PATH_ROWS
+  sparse_path_rows<T, CPL, LX, L2, LO, l1, l2, l3, WXW, WY, V>(xl, gxl, gy2, g2, w2, dot, cybuf, ctab);
+#else
+  V sv[NP], xw[NP];
   V pik = zero_packet<V>();
 #pragma unroll
   for (int p = 0; p < NP; ++p) dot[p] = sv[p] = xw[p] = zero_packet<V>();
@@ -124,6 +128,7 @@ __device__ __forceinline__ void team_path(const V* xl, V* gxl, V* gy2, const V* 
       }
     });
   });
+#endif
   if (want_w) {
     T gwv[CPL];
     unpack_packets<PK, T, CPL, 1>(dot, gwv);
@@ -145,7 +150,7 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
   using PK = Pk<T, CPL>;
   using V = typename PK::V;
   constexpr int NP = PK::NP;
-  constexpr int TW = kTeamWarps, S = kTeamStages;
+  constexpr int TW = kTeamWarps;
   constexpr int TT = canon_toff(LX, L2, LO, -1, -1, -1);  // terms, padded per path
   constexpr int kRounds = (TT + 31) / 32;
   static_assert(kRounds <= kMaxSparseRounds, "coupling program too long for the register budget");
@@ -161,13 +166,14 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int team = warp / TW, tw = warp % TW;
   const int nteams = blockDim.x / (32 * TW);
-  const int R = P.slots;
+  const int R = P.slots;       // slots of the g ring
+  const int S = P.row_stages;  // weight-row stages
   const int W = F.W;
   const int cw0 = tw * chw;  // first channel of this warp
 
   // ---- shared memory: CTA-wide coefficient table, then one region per team
   T* ctab = reinterpret_cast<T*>(smem_raw);
-  unsigned char* team_base = smem_raw + sparse_shared_bytes<T>(F) + static_cast<size_t>(team) * team_bytes<T>(F, R);
+  unsigned char* team_base = smem_raw + sparse_shared_bytes<T>(F) + static_cast<size_t>(team) * team_bytes<T>(F, S, R);
   T* wst = reinterpret_cast<T*>(team_base);                       // [S][W]
   T* gsl = wst + static_cast<size_t>(S) * W;                      // [R][gslot_elems]
   T* warp_mem = gsl + static_cast<size_t>(R) * gslot_elems + static_cast<size_t>(tw) * team_warp_elems<T>(F);
@@ -177,10 +183,10 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
   T* ybuf = gbuf + 32;
   T* gysum = gsl + static_cast<size_t>(R) * gslot_elems + static_cast<size_t>(TW) * team_warp_elems<T>(F);  // [3][TW][32]
   uint64_t* wfull = reinterpret_cast<uint64_t*>(gysum + kTeamSumBuffers * TW * 32);  // [S] row landed
-  uint64_t* gfull = wfull + S;                                                         // [R] g block landed
+  uint64_t* gfull = wfull + kTeamMaxStages;                                            // [R] g block landed
   unsigned* wdone = reinterpret_cast<unsigned*>(gfull + kTeamMaxSlots);  // [S] warps done with the row
-  unsigned* gdone = wdone + S;                                           // [R] warps done with the g block
-  unsigned* ydone = gdone + kTeamMaxSlots;                               // [3] warps that have written their gy sums
+  unsigned* gdone = wdone + kTeamMaxStages;                              // [R] warps done with the g block
+  unsigned* ydone = gdone + kTeamMaxSlots;                               // warps that have written their gy sums
 
   if (tw == 0 && lane == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&wfull[s], 1);
@@ -263,10 +269,15 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
     auto id_at = [&](int64_t p) { return p < p_end ? P.edge_ids[p] : -1; };
     auto dst_of = [&](int e) { return e >= 0 ? P.dst[e] : 0; };
     int e0 = id_at(p_begin), e1 = id_at(p_begin + 1), e2 = id_at(p_begin + 2), e3 = id_at(p_begin + 3);
+    int e4 = id_at(p_begin + 4);  // the row of the edge S <= 4 edges ahead is requested when a stage comes free
     int d0 = dst_of(e0), d1n = dst_of(e1), d2n = dst_of(e2);
+    auto edge_ahead = [&](int k) { return k == 1 ? e1 : (k == 2 ? e2 : (k == 3 ? e3 : e4)); };
     if (start_next_tile) {
       load_row(e0, st);
-      if (e1 >= 0) load_row(e1, st ^ 1);
+      for (int k = 1, stage = st; k < S; ++k) {
+        if (++stage == S) stage = 0;
+        if (edge_ahead(k) >= 0) load_row(edge_ahead(k), stage);
+      }
       for (int v = 0, slot = s; v < R && v < total_units; ++v) {
         const int de = v / nk, kind = v - de * nk;  // R <= nk, so de is 0
         load_g(kind, de == 0 ? d0 : d1n, slot);
@@ -276,7 +287,8 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
     T y_next = lane < F.Y ? P.y[static_cast<int64_t>(e0) * F.Y + lane] : T(0);
     int64_t pos = p_begin;
     int u = 0;                 // unit being consumed, counted inside the tile
-    bool refill_stage = false; // this warp sent the previous edge's row back and will refill that stage
+    int refill_stage = -1;     // this warp sent a row back from that stage and will refill it
+    int refill_edge = -1;      // with the row of this edge
 
     // The paths into output degree l3 of the current edge.
     auto unit_body = [&](auto l3c, const T* gblock, T* wrow) {
@@ -364,12 +376,12 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
           if constexpr (kind == 0) {
             // This warp sent the previous edge's row back: the store has read the stage by now, so the row of the
             // next edge can come into it.
-            if (refill_stage && alive) {
+            if (refill_stage >= 0 && alive) {
               if (lane == 0) {
                 bulk_wait_group_read_all();
-                if (pos + 1 < p_end) load_row(e1, st ^ 1);
+                if (refill_edge >= 0) load_row(refill_edge, refill_stage);
               }
-              refill_stage = false;
+              refill_stage = -1;
             }
           }
         });
@@ -388,10 +400,12 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
         last = __shfl_sync(0xffffffffu, last, 0);
         const bool final_edge = pos + 1 == p_end;
         if (last && !final_edge) {
+          const int ahead = edge_ahead(S);  // the edge that will use this stage next (-1 past the tile's end)
           if (stage_gw) {
-            refill_stage = true;  // after the next unit
-          } else if (lane == 0 && pos + 2 < p_end) {
-            load_row(e2, st);     // nothing to send back: the stage is free now
+            refill_stage = st;  // after the next unit, when the store has read the stage
+            refill_edge = ahead;
+          } else if (ahead >= 0) {
+            load_row(ahead, st);  // nothing to send back: the stage is free now
           }
         }
         if (final_edge) {
@@ -415,8 +429,9 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
           });
           reduce_tile_rows<T, (YD + 1) / 2>(red, gbuf, lane);
           // Hand-off: both warps put their sums into the edge's buffer; the last one adds them and writes gy.
-          // Three buffers in rotation: a warp can be at most two edges ahead of the other (it needs the row stage
-          // the other one releases), so a buffer is never rewritten before it has been read.
+          // One buffer more than there are row stages, in rotation: a warp cannot run further ahead of the other
+          // than the stages reach (it needs a stage the other one releases), so a buffer is never rewritten
+          // before it has been read.
           T* sums = gysum + static_cast<size_t>(sumbuf) * TW * 32;
           if (lane < YD) sums[tw * 32 + lane] = gbuf[lane];
           __syncwarp();
@@ -439,9 +454,10 @@ __global__ void __launch_bounds__(kTeamMaxTeams * kTeamWarps * 32, 1)
         e1 = e2;
         d1n = d2n;
         e2 = e3;
+        e3 = e4;
         if (pos + 3 < p_end) d2n = P.dst[e2];
-        if (pos + 4 < p_end) e3 = P.edge_ids[pos + 4];
-        st ^= 1;
+        e4 = pos + 5 < p_end ? P.edge_ids[pos + 5] : -1;
+        if (++st == S) st = 0;
       }
       if (!alive) break;
       if (want_x) {
@@ -487,20 +503,34 @@ int launch_fast_bwd_team(const luna_uvu_plan* plan, const DeviceTables& dt, cons
   int max_teams = std::min(kTeamMaxTeams, std::max(1, by_registers));
   if (plan->tuning.max_warps > 0) max_teams = std::max(1, std::min(max_teams, plan->tuning.max_warps / kTeamWarps));
   const size_t budget = static_cast<size_t>(dt.max_smem_optin);
-  int teams = 0, slots = 0;
+  // Measured on cfg2: the time follows the number of resident teams (6 teams 16.7 ms, 5 teams 19.2 ms, 4 teams
+  // 20.9 ms), not the number of row stages (2, 3 and 4 stages with 4 teams: all 20.9 ms), so shared memory goes to
+  // teams first and two stages are the default.
+  int want_stages = plan->tuning.row_stages > 0 ? std::max(2, std::min(kTeamMaxStages, plan->tuning.row_stages)) : 2;
+  int teams = 0, slots = 0, stages = 0;
   size_t block_bytes = 0;
-  for (int t = max_teams; t >= 1 && teams == 0; --t)
-    for (int depth = std::min(kTeamMaxSlots, f.nkinds); depth >= std::min(2, f.nkinds); --depth) {
-      const size_t bytes = sparse_shared_bytes<T>(f) + t * team_bytes<T>(f, depth);
-      if (bytes > budget) continue;
-      teams = t;
-      slots = depth;
-      block_bytes = bytes;
-      break;
-    }
+  for (int st = want_stages; st >= 2 && teams == 0; --st)
+    for (int t = max_teams; t >= std::min(max_teams, 4) && teams == 0; --t)
+      for (int depth = std::min(kTeamMaxSlots, f.nkinds); depth >= std::min(2, f.nkinds); --depth) {
+        const size_t bytes = sparse_shared_bytes<T>(f) + t * team_bytes<T>(f, st, depth);
+        if (bytes > budget) continue;
+        teams = t;
+        slots = depth;
+        stages = st;
+        block_bytes = bytes;
+        break;
+      }
+  for (int t = std::min(max_teams, 3); t >= 1 && teams == 0; --t) {  // very wide rows: fewer teams, two stages
+    const size_t bytes = sparse_shared_bytes<T>(f) + t * team_bytes<T>(f, 2, std::min(2, f.nkinds));
+    if (bytes > budget) continue;
+    teams = t;
+    slots = std::min(2, f.nkinds);
+    stages = 2;
+    block_bytes = bytes;
+  }
   if (teams == 0) return fail(LUNA_ERR_UNSUPPORTED, "team backward needs more shared memory than the device has");
   P.slots = slots;
-  P.row_stages = kTeamStages;
+  P.row_stages = stages;
   // Tiles of about 96 edges: small enough that static round-robin balances the teams, large enough that the few
   // microseconds a team spends filling its pipeline at the start of a tile do not matter.
   const int64_t rows = P.num_src_nodes;

@@ -61,6 +61,8 @@ __device__ __forceinline__ float vfma(float a, float b, float c) { return fmaf(a
 __device__ __forceinline__ double vfma(double a, double b, double c) { return fma(a, b, c); }
 __device__ __forceinline__ float vmul(float a, float b) { return a * b; }
 __device__ __forceinline__ double vmul(double a, double b) { return a * b; }
+__device__ __forceinline__ float vadd(float a, float b) { return a + b; }
+__device__ __forceinline__ double vadd(double a, double b) { return a + b; }
 __device__ __forceinline__ float hsum(float a) { return a; }
 __device__ __forceinline__ double hsum(double a) { return a; }
 __device__ __forceinline__ float make_packet(const float* vals, float) { return vals[0]; }

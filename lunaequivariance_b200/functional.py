@@ -1,7 +1,8 @@
-"""Functional entry points: ``prepare_tensor_product`` and ``tensor_product_conv``.
+"""Functional entry points: ``prepare_tensor_product``, ``tensor_product_conv`` and ``tensor_product``.
 
-Same names, arguments and error messages as the reference (``src/lunatp/interface.py:147-262``), restricted to what
-the UVU convolution path needs: ``convolution=True`` with ``uvu`` instructions and explicit per-edge weights.
+Same names, arguments and error messages as the reference (``src/lunatp/interface.py:147-262``), restricted to
+``uvu`` instructions: the graph convolution with explicit per-edge weights (``convolution=True``) and the tensor
+product of independent items (``convolution=False``).
 
 ``TensorProductConv`` and ``prepare_tensor_product`` accept the same three kinds of first argument (irreps strings,
 a tensor-product-like object, prebuilt path metadata).  Both go through ``resolve_source`` below, which sorts the
@@ -21,6 +22,7 @@ import torch
 from .conv import LunaTPUVUConv, create_uvu_conv_operator
 from .irreps import as_irreps
 from .paths import TensorProductPaths
+from .tensor_product import LunaTPUVU
 
 PATH_OPTIONS = ("in1_var", "in2_var", "out_var", "irrep_normalization", "path_normalization")
 _MODES = frozenset(("uuu", "uvu", "uvw"))
@@ -84,11 +86,11 @@ def prepare_tensor_product(irreps_in1, irreps_in2=None, irreps_out=None, instruc
         copy(irreps_in1) if isinstance(irreps_in1, TensorProductPaths) else irreps_in1, build=build, mode=mode,
         metadata_message='Metadata requires convolution=True and mode="uuu" or "uvu"',
         mode_message="Tensor products require one connection mode: uuu, uvu or uvw")
+    require_uvu(resolved.mode, "mode")
     if not resolved.from_metadata:
         resolved.source.dtype = dtype
         if not convolution:
-            raise NotImplementedError("this build provides the uvu convolution only (convolution=True)")
-    require_uvu(resolved.mode, "mode")
+            return LunaTPUVU(resolved.source, dtype=dtype)
     return create_uvu_conv_operator(resolved.source, dtype=dtype)
 
 
@@ -121,4 +123,30 @@ def tensor_product_conv(x, edge_attr, weight=None, *, graph, irreps_in1=None, ir
     return config.run(config, x, edge_attr, weight, graph=graph, **kwargs)
 
 
-__all__ = ["prepare_tensor_product", "tensor_product_conv"]
+def tensor_product(x, y, weight=None, *, irreps_in1=None, irreps_in2=None, irreps_out=None, instructions=None,
+                   in1_var=None, in2_var=None, out_var=None, irrep_normalization=None, path_normalization=None,
+                   shared_weights=False, config=None):
+    """Independent tensor products, one per item; shared weights are ``[weight_numel]``, external weights one row
+    per item."""
+    if config is None:
+        if None in (irreps_in1, irreps_in2, irreps_out, instructions):
+            raise TypeError("Supply irreps and instructions, or a prepared config")
+        config = _prepared_item_product(
+            *(str(as_irreps(r)) for r in (irreps_in1, irreps_in2, irreps_out)),
+            tuple(tuple(i) for i in instructions), _hashable(in1_var), _hashable(in2_var), _hashable(out_var),
+            irrep_normalization, path_normalization, shared_weights, x.dtype)
+    if not isinstance(config, LunaTPUVU):
+        raise TypeError("config must come from prepare_tensor_product(..., convolution=False)")
+    return config.run(config, x, y, weight)
+
+
+@lru_cache(maxsize=128)
+def _prepared_item_product(irreps_in1, irreps_in2, irreps_out, instructions, in1_var, in2_var, out_var,
+                           irrep_normalization, path_normalization, shared_weights, dtype):
+    return prepare_tensor_product(
+        irreps_in1, irreps_in2, irreps_out, instructions, in1_var=in1_var, in2_var=in2_var, out_var=out_var,
+        irrep_normalization=irrep_normalization, path_normalization=path_normalization,
+        shared_weights=shared_weights, dtype=dtype, convolution=False)
+
+
+__all__ = ["prepare_tensor_product", "tensor_product_conv", "tensor_product"]

@@ -11,9 +11,10 @@ from collections.abc import Mapping
 import torch
 
 from .conv import create_uvu_conv_operator
-from .functional import require_uvu, resolve_source, tensor_product_conv
+from .functional import require_uvu, resolve_source, tensor_product, tensor_product_conv
 from .graph import make_graph
 from .paths import TensorProductConfig
+from .tensor_product import LunaTPUVU
 from .spherical_harmonics import UNSET, SphericalHarmonicsConfig, parse_irreps, spherical_harmonics
 
 
@@ -90,6 +91,65 @@ class TensorProductConv(torch.nn.Module):
         return tensor_product_conv(x, edge_attr, weight, graph=graph, config=self.op, **kwargs)
 
 
+class TensorProduct(torch.nn.Module):
+    """UVU tensor product of independent items with e3nn path and normalisation arguments.
+
+    Pass irreps and ``uvu`` instructions, or an existing tensor-product-like module/configuration
+    (``src/modules/tensorproduct.py:19-117``).  Weights are one row per item, or a shared vector when the paths
+    have ``shared_weights=True`` (with ``internal_weights=True`` the module owns it).
+    """
+
+    def __init__(self, irreps_in1, irreps_in2=None, irreps_out=None, instructions=None, in1_var=None, in2_var=None,
+                 out_var=None, irrep_normalization=None, path_normalization=None, internal_weights=None,
+                 shared_weights=None, *, dtype=None):
+        super().__init__()
+        options = dict(in1_var=in1_var, in2_var=in2_var, out_var=out_var, irrep_normalization=irrep_normalization,
+                       path_normalization=path_normalization, internal_weights=internal_weights,
+                       shared_weights=shared_weights)
+        if isinstance(irreps_in1, torch.nn.Module) and not all(
+                v is None for v in (irreps_in2, irreps_out, instructions, *options.values())):
+            raise TypeError("Pass either an existing tensor product or irreps and path options")
+
+        def build():
+            if None in (irreps_in2, irreps_out, instructions):
+                raise TypeError("irreps_in2, irreps_out and instructions are required")
+            product = TensorProductConfig(irreps_in1, irreps_in2, irreps_out, instructions, **options)
+            if dtype is not None and product.weight.dtype != dtype:
+                product.to(dtype=dtype)
+            return product
+
+        resolved = resolve_source(
+            irreps_in1, build=build, mode=None, metadata_message="TensorProduct takes irreps or a tensor product",
+            mode_message="TensorProduct requires one connection mode: uuu, uvu or uvw")
+        require_uvu(resolved.mode, "mode")
+        source = resolved.source
+        self.mode = resolved.mode
+        self.op = LunaTPUVU(source, dtype=dtype)
+        self.tp = source
+        for name in ("irreps_in1", "irreps_in2", "irreps_out", "instructions", "weight_numel", "internal_weights",
+                     "shared_weights"):
+            setattr(self, name, getattr(source, name))
+        self.train(getattr(source, "training", True))
+
+    @property
+    def weight(self):
+        return getattr(self.tp, "weight", None)
+
+    def _apply(self, fn, recurse=True):
+        dtype = fn(torch.empty(0, dtype=self.op.compute_dtype)).dtype
+        if dtype not in (torch.float32, torch.float64):
+            raise ValueError("Tensor products support float32 and float64 inputs")
+        result = super()._apply(fn, recurse=recurse)
+        if dtype != self.op.compute_dtype:
+            self.op = LunaTPUVU(self.tp, dtype=dtype, index_bits=self.op.index_bits)
+        return result
+
+    def forward(self, x, y, weight=None):
+        if weight is None and self.internal_weights:
+            weight = self.weight
+        return tensor_product(x, y, weight, config=self.op)
+
+
 _SH_DTYPES = (torch.float16, torch.bfloat16, torch.float32, torch.float64)
 
 
@@ -151,4 +211,4 @@ class SphericalHarmonics(torch.nn.Module):
 
 LunaEqSphericalHarmonics = SphericalHarmonics
 
-__all__ = ["TensorProductConv", "SphericalHarmonics", "LunaEqSphericalHarmonics"]
+__all__ = ["TensorProductConv", "TensorProduct", "SphericalHarmonics", "LunaEqSphericalHarmonics"]

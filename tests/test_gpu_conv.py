@@ -210,8 +210,10 @@ def test_input_validation_errors():
         conv(x.double(), y, w, graph=graph)
     with pytest.raises(ValueError):
         conv(x[:, :-1], y, w, graph=graph)
-    with pytest.raises(NotImplementedError):
-        conv(x, y, w, graph=graph, env=torch.ones(2, device=DEVICE))
+    with pytest.raises(ValueError):
+        conv(x, y, w, graph=graph, env=torch.ones(3, device=DEVICE))
+    with pytest.raises(TypeError):
+        conv(x, y, w, graph=graph, env=torch.ones(2, device=DEVICE, dtype=torch.float64))
     with pytest.raises(RuntimeError, match="CUDA is required"):
         conv(x.cpu(), y.cpu(), w.cpu(), graph=graph)
 
