@@ -327,6 +327,7 @@ Tuning tuning_from_environment() {
   };
   t.no_canon = std::getenv("LUNA_B200_NO_CANON") != nullptr;
   t.no_sparse = std::getenv("LUNA_B200_NO_SPARSE") != nullptr;
+  t.no_plain = std::getenv("LUNA_B200_NO_PLAIN") != nullptr;
   if (const char* kind = std::getenv("LUNA_B200_BWD_KERNEL"))
     t.bwd_kernel = kind[0] == 'r' ? 1 : (kind[0] == 'u' ? 2 : (kind[0] == 't' ? 3 : 0));
   t.max_warps = static_cast<int>(std::max(0ll, number("LUNA_B200_MAXW")));

@@ -105,12 +105,13 @@ struct FastMeta {
 // variables, read once when the plan is created (never on a launch path):
 //   LUNA_B200_NO_CANON=1        canonical path lists run the kernels that loop over run-time path tables
 //   LUNA_B200_NO_SPARSE=1       backward without the compiled-in coupling patterns
+//   LUNA_B200_NO_PLAIN=1        backward without the kernels that have the layout compiled in
 //   LUNA_B200_BWD_KERNEL=row|units|team   data-movement variant of the backward kernel with compiled-in patterns
 //   LUNA_B200_MAXW=n            cap on warps per CTA
 //   LUNA_B200_ROW_STAGES=n      cap on weight-row stages of the row-staged backward
 //   LUNA_B200_EPW=n             target edges per warp when a graph needs several waves
 struct Tuning {
-  bool no_canon = false, no_sparse = false;
+  bool no_canon = false, no_sparse = false, no_plain = false;
   int bwd_kernel = 0;  // 0 automatic, 1 row stages, 2 unit ring, 3 warp teams
   int max_warps = 0;   // 0: no cap
   int row_stages = 0;  // 0: no cap

@@ -529,10 +529,11 @@ __global__ void reduce_gy_partial(const T* __restrict__ partial, T* __restrict__
 namespace luna {
 namespace fastk {
 
-// Warp-team kernel (uvu_fast_bwd_team.cuh), FP32 with 128 channels; compiled in its own translation unit, which
-// dispatches on the degree shape of the canonical path list.
-int launch_fast_bwd_team_f32(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph,
-                             const BwdParams<float>& P, bool has_gy, bool wxw, cudaStream_t stream);
+// Kernels with a compile-time layout (uvu_fast_bwd_plain.cuh), one translation unit per (T, CPL).  Returns
+// LUNA_ERR_UNSUPPORTED if the plan's layout is not the compile-time one.
+template <typename T, int CPL>
+int launch_fast_bwd_plain_any(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph,
+                              const BwdParams<T>& P, bool teams, cudaStream_t stream);
 
 template <typename T, int CPL, int LX, int LO, int L2>
 int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
@@ -583,15 +584,18 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     // compiled-in coupling patterns, if the plan's terms have them
     if constexpr (sparse_shape_ok<LX, (L2 < 0 ? 0 : L2), LO>()) {
       const int variant = fast_bwd_variant(plan);
-      if constexpr (std::is_same<T, float>::value) {
-        if (variant == LUNA_BWD_WARP_TEAMS) {
-          const int rc = launch_fast_bwd_team_f32(plan, dt, graph, P, gy != nullptr, wxw, stream);
-          if (rc != LUNA_OK) return rc;
-          launched = true;
-        }
+      // The call training makes all the time - every gradient, nothing accumulated, one warp pass per block - has
+      // kernels with a compile-time layout, with one warp or a team of two per edge.
+      const bool plain = gx != nullptr && gy != nullptr && gw != nullptr && !acc_x && !acc_y && !acc_w &&
+                         f.chunks == 1 && (variant == LUNA_BWD_ROW_STAGES || variant == LUNA_BWD_WARP_TEAMS) &&
+                         !plan->tuning.no_plain;
+      if (plain) {
+        const int rc = launch_fast_bwd_plain_any<T, CPL>(plan, dt, graph, P, variant == LUNA_BWD_WARP_TEAMS, stream);
+        if (rc == LUNA_OK) launched = true;
+        else if (rc != LUNA_ERR_UNSUPPORTED) return rc;
       }
-      if (variant == LUNA_BWD_ROW_STAGES || variant == LUNA_BWD_UNIT_RING) {
-        const bool rows = variant == LUNA_BWD_ROW_STAGES;
+      if (!launched && variant != LUNA_BWD_STAGED_TABLES) {
+        const bool rows = variant != LUNA_BWD_UNIT_RING;
         const int rc = rows ? launch_fast_bwd_sparse<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream)
                             : launch_fast_bwd_units<T, CPL, LX, (L2 < 0 ? 0 : L2), LO>(plan, dt, graph, P, gy != nullptr, wxw, stream);
         if (rc != LUNA_OK) return rc;

@@ -202,10 +202,10 @@ __device__ __forceinline__ void sparse_path_rows(const V* xl, V* gxl, V* gy2, co
 // Warps per CTA at most (caps the registers per thread): FP32 with at most two channels per lane needs fewer
 // registers and runs up to 12 warps (168 registers), everything else 8 (255).
 #ifndef LUNA_SPARSE_WARPS_SMALL
-#define LUNA_SPARSE_WARPS_SMALL 12
+#define LUNA_SPARSE_WARPS_SMALL 16
 #endif
-// Shapes up to degree 2 keep far less state per lane (9 x and gx packets, 9 gy accumulators, a short program);
-// LUNA_SPARSE_WARPS_SMALL is their warp limit.
+// Shapes up to degree 2 keep far less state per lane (9 x and gx packets, 9 gy accumulators, a short program) and run
+// 16 warps at 128 registers (measured on the 64-channel degree-2 workload: 29.4 ms at 12 warps, 26.6 ms at 16).
 template <typename T, int CPL, int LX = 3, int L2 = 3, int LO = 3>
 __host__ __device__ constexpr int sparse_max_warps() {
   if (sizeof(T) == 4 && CPL <= 2) return (LX <= 2 && L2 <= 2 && LO <= 2) ? LUNA_SPARSE_WARPS_SMALL : 12;
@@ -347,62 +347,12 @@ __global__ void __launch_bounds__(sparse_max_warps<T, CPL, LX, L2, LO>() * 32, 1
   // their gradients when the row is staged back); w_goff: their global offset.
   auto path_body = [&](auto l1c, auto l2c, auto l3c, const V* g2, T* wq, int64_t w_goff) {
     constexpr int l1 = decltype(l1c)::value, l2 = decltype(l2c)::value, l3 = decltype(l3c)::value;
-    using PT = CgPattern<l1, l2, l3>;
-    constexpr int n = PT::n;
-    constexpr int toff = canon_toff(LX, L2, LO, l1, l2, l3);
     V w2[NP];  // a lane's consecutive channels are already adjacent in memory
     load_lane_packets<PK, T, CPL>(wq, w2);
     const V* xl = &xr[l1 * l1 * NP];
     V* gxl = &gxr[l1 * l1 * NP];
     V dot[NP];
-#ifdef LUNA_PATH_ROWS
     sparse_path_rows<T, CPL, LX, L2, LO, l1, l2, l3, WXW, WY, V>(xl, gxl, gy2, g2, w2, dot, cybuf, ctab);
-#else
-    V sv[NP], xw[NP];
-    V pik = zero_packet<V>();
-#pragma unroll
-    for (int p = 0; p < NP; ++p) dot[p] = sv[p] = xw[p] = zero_packet<V>();
-    static_for<0, (n + 3) / 4>([&](auto gc) {
-      constexpr int group = decltype(gc)::value;
-      T cy4[4], cc4[4];
-      if constexpr (WXW) load_four<T>(cybuf + toff + 4 * group, cy4);
-      if constexpr (WY) load_four<T>(ctab + toff + 4 * group, cc4);
-      static_for<0, 4>([&](auto uc) {
-        constexpr int t = 4 * group + decltype(uc)::value;
-        if constexpr (t < n) {
-          constexpr int i = PT::t[t].i, j = PT::t[t].j, k = PT::t[t].k;
-          constexpr bool row_first = t == 0 || PT::t[t == 0 ? 0 : t - 1].i != i;
-          constexpr bool row_last = t == n - 1 || PT::t[t == n - 1 ? t : t + 1].i != i;
-          constexpr bool ik_first = row_first || PT::t[t == 0 ? 0 : t - 1].k != k;
-          if constexpr (WY) {
-            if constexpr (row_first) {
-#pragma unroll
-              for (int p = 0; p < NP; ++p) xw[p] = vmul(xl[i * NP + p], w2[p]);
-            }
-            if constexpr (ik_first) {
-              pik = vmul(xw[0], g2[k * NP]);
-#pragma unroll
-              for (int p = 1; p < NP; ++p) pik = vfma(xw[p], g2[k * NP + p], pik);
-            }
-            gy2[l2 * l2 + j] = vfma(bcast_packet(cc4[t % 4], V{}), pik, gy2[l2 * l2 + j]);
-          }
-          if constexpr (WXW) {
-#pragma unroll
-            for (int p = 0; p < NP; ++p)
-              sv[p] = row_first ? vmul(bcast_packet(cy4[t % 4], V{}), g2[k * NP + p])
-                                : vfma(bcast_packet(cy4[t % 4], V{}), g2[k * NP + p], sv[p]);
-            if constexpr (row_last) {
-#pragma unroll
-              for (int p = 0; p < NP; ++p) {
-                gxl[i * NP + p] = vfma(w2[p], sv[p], gxl[i * NP + p]);
-                dot[p] = vfma(xl[i * NP + p], sv[p], dot[p]);
-              }
-            }
-          }
-        }
-      });
-    });
-#endif
     if (want_w) {
       T gwv[CPL];
       unpack_packets<PK, T, CPL, 1>(dot, gwv);
