@@ -99,8 +99,7 @@ typedef enum {
   LUNA_BWD_TABLE_DRIVEN = 0, /* one thread per output element, any configuration */
   LUNA_BWD_STAGED_TABLES = 1, /* staged kernel that reads the path list from tables */
   LUNA_BWD_ROW_STAGES = 2,    /* compiled-in coupling patterns, one warp per edge, whole weight rows staged */
-  LUNA_BWD_UNIT_RING = 3,     /* compiled-in coupling patterns, one warp per edge, (edge, degree) units in a ring */
-  LUNA_BWD_WARP_TEAMS = 4     /* compiled-in coupling patterns, several warps share an edge's staged rows */
+  LUNA_BWD_UNIT_RING = 3      /* compiled-in coupling patterns, one warp per edge, (edge, degree) units in a ring */
 } luna_bwd_variant;
 LUNA_API int64_t luna_uvu_plan_query(const luna_uvu_plan* plan, int what);
 

@@ -175,8 +175,8 @@ class LunaTPUVUConv:
     @property
     def backward_variant(self) -> str:
         """Which first-order backward kernel aligned inputs get: ``generic`` (table-driven), ``tables`` (staged,
-        path list read from tables), ``row``, ``units`` or ``team`` (compiled-in coupling patterns)."""
-        return ("generic", "tables", "row", "units", "team")[self._plan.query(7)]
+        path list read from tables), ``row`` or ``units`` (compiled-in coupling patterns)."""
+        return ("generic", "tables", "row", "units")[self._plan.query(7)]
 
     def check_status(self, device=None) -> None:
         """Raise ``RuntimeError`` if a kernel of this operator gave up a bounded wait since the last check.

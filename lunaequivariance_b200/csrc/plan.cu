@@ -329,10 +329,11 @@ Tuning tuning_from_environment() {
   t.no_sparse = std::getenv("LUNA_B200_NO_SPARSE") != nullptr;
   t.no_plain = std::getenv("LUNA_B200_NO_PLAIN") != nullptr;
   if (const char* kind = std::getenv("LUNA_B200_BWD_KERNEL"))
-    t.bwd_kernel = kind[0] == 'r' ? 1 : (kind[0] == 'u' ? 2 : (kind[0] == 't' ? 3 : 0));
+    t.bwd_kernel = kind[0] == 'r' ? 1 : (kind[0] == 'u' ? 2 : 0);
   t.max_warps = static_cast<int>(std::max(0ll, number("LUNA_B200_MAXW")));
   t.row_stages = static_cast<int>(std::max(0ll, number("LUNA_B200_ROW_STAGES")));
   t.edges_per_warp = std::max(0ll, number("LUNA_B200_EPW"));
+  t.fwd_tile_edges = std::max(0ll, number("LUNA_B200_FWD_TILE"));
   return t;
 }
 

@@ -106,16 +106,19 @@ struct FastMeta {
 //   LUNA_B200_NO_CANON=1        canonical path lists run the kernels that loop over run-time path tables
 //   LUNA_B200_NO_SPARSE=1       backward without the compiled-in coupling patterns
 //   LUNA_B200_NO_PLAIN=1        backward without the kernels that have the layout compiled in
-//   LUNA_B200_BWD_KERNEL=row|units|team   data-movement variant of the backward kernel with compiled-in patterns
+//   LUNA_B200_BWD_KERNEL=row|units   data-movement variant of the backward kernel with compiled-in patterns
 //   LUNA_B200_MAXW=n            cap on warps per CTA
 //   LUNA_B200_ROW_STAGES=n      cap on weight-row stages of the row-staged backward
-//   LUNA_B200_EPW=n             target edges per warp when a graph needs several waves
+//   LUNA_B200_EPW=n             backward: edges per tile of source nodes (kernels with a compile-time layout), target
+//                               edges per warp when a graph needs several waves (the others)
+//   LUNA_B200_FWD_TILE=n        forward: edges per tile of destination nodes
 struct Tuning {
   bool no_canon = false, no_sparse = false, no_plain = false;
-  int bwd_kernel = 0;  // 0 automatic, 1 row stages, 2 unit ring, 3 warp teams
+  int bwd_kernel = 0;  // 0 automatic, 1 row stages, 2 unit ring
   int max_warps = 0;   // 0: no cap
   int row_stages = 0;  // 0: no cap
   int64_t edges_per_warp = 0;  // 0: the kernel's default
+  int64_t fwd_tile_edges = 0;  // 0: the kernel's default
 };
 Tuning tuning_from_environment();
 

@@ -74,12 +74,7 @@ extern template int launch_fast_bwd<double, 2>(LUNA_BWD_SIG(double));
 
 bool fast_available() { return true; }
 
-namespace fastk {
-bool team_available() { return true; }
-}  // namespace fastk
-
 int fast_bwd_variant(const luna_uvu_plan* plan) {
-  using fastk::team_available;
   if (!plan->fast_ok || plan->force_generic) return LUNA_BWD_TABLE_DRIVEN;
   const FastMeta& f = plan->fast;
   const int lx = f.LX, lo = f.LO, l2 = f.canon_l2;
@@ -88,17 +83,12 @@ int fast_bwd_variant(const luna_uvu_plan* plan) {
                                                          (lx == 3 && l2 == 3 && lo == 3) || (lx == 1 && l2 == 1 && lo == 1));
   if (!compiled_shape || f.sparse_terms <= 0 || plan->tuning.no_sparse) return LUNA_BWD_STAGED_TABLES;
   const size_t elem = plan->dtype == LUNA_F64 ? 8 : 4;
-  // Warp teams: two warps split an edge's paths; needs one warp pass per block.
-  const bool team_ok = team_available() && f.chunks == 1;
   // Row stages pay off when an edge's weight row is one long contiguous piece for the CTA; short rows and rows
   // split into channel chunks go through the unit ring.
   const bool rows_ok = f.chunks == 1;
-  // Measured on the 128-channel degree-3 workload the warp teams (12 warps, 40 % more instructions per edge) and the
-  // row stages (8 warps) are within 3 % of each other; row stages are the default, teams on request.
   int variant = rows_ok && static_cast<size_t>(f.w_stage_elems) * elem >= 2560 ? LUNA_BWD_ROW_STAGES : LUNA_BWD_UNIT_RING;
   if (plan->tuning.bwd_kernel == 1) variant = LUNA_BWD_ROW_STAGES;
   if (plan->tuning.bwd_kernel == 2) variant = LUNA_BWD_UNIT_RING;
-  if (plan->tuning.bwd_kernel == 3 && team_ok) variant = LUNA_BWD_WARP_TEAMS;
   return variant;
 }
 

@@ -56,7 +56,6 @@ struct BwdParams {
   int64_t num_src_nodes, num_edges;
   int slots;
   int row_stages;  // kernel with compiled-in patterns: weight-row stages per warp
-  int64_t tile_nodes;  // warp-team kernel: source nodes per tile
   int acc_x, acc_y, acc_w;
 };
 
@@ -533,7 +532,7 @@ namespace fastk {
 // LUNA_ERR_UNSUPPORTED if the plan's layout is not the compile-time one.
 template <typename T, int CPL>
 int launch_fast_bwd_plain_any(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph,
-                              const BwdParams<T>& P, bool teams, cudaStream_t stream);
+                              const BwdParams<T>& P, cudaStream_t stream);
 
 template <typename T, int CPL, int LX, int LO, int L2>
 int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const luna_graph* graph, const T* x,
@@ -557,7 +556,6 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.sp_c = nullptr;
   P.sp_j = nullptr;
   P.row_stages = 0;
-  P.tile_nodes = 1;
   P.status = dt.status;
   P.num_src_nodes = graph->num_src_nodes > 0 ? graph->num_src_nodes : graph->num_nodes;
   P.num_edges = graph->num_edges;
@@ -585,12 +583,11 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     if constexpr (sparse_shape_ok<LX, (L2 < 0 ? 0 : L2), LO>()) {
       const int variant = fast_bwd_variant(plan);
       // The call training makes all the time - every gradient, nothing accumulated, one warp pass per block - has
-      // kernels with a compile-time layout, with one warp or a team of two per edge.
+      // kernels with a compile-time layout.
       const bool plain = gx != nullptr && gy != nullptr && gw != nullptr && !acc_x && !acc_y && !acc_w &&
-                         f.chunks == 1 && (variant == LUNA_BWD_ROW_STAGES || variant == LUNA_BWD_WARP_TEAMS) &&
-                         !plan->tuning.no_plain;
+                         f.chunks == 1 && variant == LUNA_BWD_ROW_STAGES && !plan->tuning.no_plain;
       if (plain) {
-        const int rc = launch_fast_bwd_plain_any<T, CPL>(plan, dt, graph, P, variant == LUNA_BWD_WARP_TEAMS, stream);
+        const int rc = launch_fast_bwd_plain_any<T, CPL>(plan, dt, graph, P, stream);
         if (rc == LUNA_OK) launched = true;
         else if (rc != LUNA_ERR_UNSUPPORTED) return rc;
       }

@@ -1,7 +1,9 @@
 // Staged forward-shaped kernel (free argument g):  out[t] = sum_{e: dst e = t} sum_p w_p * (M^p(y_e)^T x[src e]).
 //
-// One warp owns a contiguous range of destination nodes (balanced by edge count) and therefore a contiguous range
-// of the destination-sorted edge list: a warp-segmented reduction with register accumulators and no atomics.  Per
+// Destination nodes are cut into small tiles of consecutive nodes, and warp q of Q takes tiles q, q + Q, ...: a tile
+// is a contiguous piece of the destination-sorted edge list, reduced by one warp with register accumulators and no
+// atomics, and at any moment the resident warps work on neighbouring destination nodes, so that for a spatially
+// ordered graph the x[src] rows they gather are the same few thousand rows and stay in L2.  Per
 // edge, lanes issue 1-D bulk copies (cp.async.bulk, completion on an mbarrier) of the edge's weight row and of the
 // gathered x[src] row into the warp's ring of shared-memory stages; the warp then reads them with 128-bit shared
 // loads while later edges are in flight.  A lane owns CPL consecutive channels of every block.
@@ -23,10 +25,20 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include "cg_patterns.h"
 #include "uvu_packets.cuh"
 
 namespace luna {
 namespace fastk {
+
+// Whether the coupling tensor with pattern PT has a non-zero entry C[i][j][k] for some j: only those (i, k) have a
+// non-zero entry in an edge's coupling matrix.
+template <typename PT>
+__host__ __device__ constexpr bool pattern_has_ik(int i, int k) {
+  for (int t = 0; t < PT::n; ++t)
+    if (PT::t[t].i == i && PT::t[t].k == k) return true;
+  return false;
+}
 
 template <typename T>
 struct FwdParams {
@@ -41,6 +53,7 @@ struct FwdParams {
   const T* ell_c;
   int* status;
   int64_t num_nodes, num_edges;
+  int64_t tile_nodes;  // destination nodes per tile
   int stages;
   int accumulate;
 };
@@ -109,15 +122,11 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
 
   const int chw = 32 * CPL;
   const int c0 = blockIdx.y * chw;  // first channel of this warp's chunk
-  const int64_t E = P.num_edges, N = P.num_nodes;
+  const int64_t N = P.num_nodes;
   const int nwarps = blockDim.x >> 5;
   const int64_t total_warps = static_cast<int64_t>(gridDim.x) * nwarps;
   const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * nwarps + warp;
-  const int64_t bound_lo = E * gwarp / total_warps, bound_hi = E * (gwarp + 1) / total_warps;
-  const int64_t n_lo = warp_lower_bound(P.dst_rowptr, N, bound_lo, lane);
-  const int64_t n_hi = gwarp == total_warps - 1 ? N : warp_lower_bound(P.dst_rowptr, N, bound_hi, lane);
-  if (n_lo >= n_hi) return;
-  const int64_t e_begin = P.dst_rowptr[n_lo], e_end = P.dst_rowptr[n_hi];
+  const int64_t num_tiles = (N + P.tile_nodes - 1) / P.tile_nodes;
 
   // Lane `pi` issues copy piece `pi` of every edge; its description stays in registers.
   const uint32_t stage_bytes = static_cast<uint32_t>(stage_elems * sizeof(T));
@@ -142,24 +151,21 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
     }
   };
 
-  for (int s = 0; s < stages; ++s)
-    if (e_begin + s < e_end) issue(e_begin + s, P.src[e_begin + s], s);
-  // source node of the edge that will be issued in the next iteration, fetched one iteration early
-  int src_ahead = e_begin + stages < e_end ? P.src[e_begin + stages] : 0;
-
-  T y_next = (lane < F.Y && e_begin < e_end) ? P.y[e_begin * F.Y + lane] : T(0);
   constexpr int AR = (LO + 1) * (LO + 1) * NP;
   constexpr int XR = (LX + 1) * (LX + 1) * NP;
   V acc[AR];  // packet (l3, k, p) at l3 * l3 * NP + k * NP + p
-  int64_t e = e_begin;
-  int s = 0;
-  uint32_t parity = 0;
+  int64_t e = 0, e_end = 0;
+  int s = 0;            // stage of the next edge; the ring keeps turning from one tile to the next
+  uint32_t parity = 0;  // phase of that stage's barrier
   bool alive = true;
 
-  // out_k += sum_i M[i][k] * (x_i * w) for one path; the matrix is stored once and broadcast into both halves
-  auto path_body = [&](auto l1c, auto l3c, const T* wq, const T* matrix, const V* xl, V* al) {
-    constexpr int l1 = decltype(l1c)::value, l3 = decltype(l3c)::value;
+  // out_k += sum_i M[i][k] * (x_i * w) for one path; the matrix is stored once and broadcast into both halves.
+  // With a compile-time degree l2 (canonical lists) the entries that the coupling tensor leaves zero for every y -
+  // about a quarter of them - are skipped.
+  auto path_body = [&](auto l1c, auto l2c, auto l3c, const T* wq, const T* matrix, const V* xl, V* al) {
+    constexpr int l1 = decltype(l1c)::value, l2 = decltype(l2c)::value, l3 = decltype(l3c)::value;
     constexpr int d1 = 2 * l1 + 1, d3 = 2 * l3 + 1, d3p = d3 + 1;
+    using PT = CgPattern<l1, (l2 < 0 ? 0 : l2), l3>;
     V w2[NP];  // a lane's consecutive channels are already adjacent in memory
     load_lane_packets<PK, T, CPL>(wq, w2);
     static_for<0, d1>([&](auto ic) {
@@ -169,11 +175,30 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
 #pragma unroll
       for (int p = 0; p < NP; ++p) {
         const V xw = vmul(xl[i * NP + p], w2[p]);
-#pragma unroll
-        for (int k = 0; k < d3; ++k) al[k * NP + p] = vfma(bcast_packet(mrow[k], V{}), xw, al[k * NP + p]);
+        static_for<0, d3>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          if constexpr (l2 < 0 || pattern_has_ik<PT>(i, k))
+            al[k * NP + p] = vfma(bcast_packet(mrow[k], V{}), xw, al[k * NP + p]);
+        });
       }
     });
   };
+
+#pragma unroll 1
+  for (int64_t tile = gwarp; tile < num_tiles && alive; tile += total_warps) {
+  const int64_t n_lo = tile * P.tile_nodes;
+  const int64_t n_hi = n_lo + P.tile_nodes < N ? n_lo + P.tile_nodes : N;
+  const int64_t e_begin = P.dst_rowptr[n_lo];
+  e_end = P.dst_rowptr[n_hi];
+  e = e_begin;
+  // all stages are empty here: fill them in ring order from the current one
+  for (int d = 0, stage = s; d < stages; ++d) {
+    if (e_begin + d < e_end) issue(e_begin + d, P.src[e_begin + d], stage);
+    if (++stage == stages) stage = 0;
+  }
+  // source node of the edge that will be issued in the next iteration, fetched one iteration early
+  int src_ahead = e_begin + stages < e_end ? P.src[e_begin + stages] : 0;
+  T y_next = (lane < F.Y && e_begin < e_end) ? P.y[e_begin * F.Y + lane] : T(0);
 
   for (int64_t n = n_lo; n < n_hi && alive; ++n) {
     const int64_t ee = P.dst_rowptr[n + 1];
@@ -222,14 +247,14 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
             static_for<0, (L2 < 0 ? 0 : L2) + 1>([&](auto l2c) {
               constexpr int l2 = decltype(l2c)::value;
               if constexpr (canon_ok(LX, L2, LO, l1, l2, l3))
-                path_body(l1c, l3c, wl + canon_wrank(LX, L2, LO, l1, l2, l3) * chw,
+                path_body(l1c, l2c, l3c, wl + canon_wrank(LX, L2, LO, l1, l2, l3) * chw,
                           mbuf + canon_moff(LX, L2, LO, l1, l2, l3), xl, al);
             });
           } else {
             const int q_end = F.pair_ptr[l3 * (kMaxFastL + 1) + l1 + 1];
 #pragma unroll 1
             for (int q = F.pair_ptr[l3 * (kMaxFastL + 1) + l1]; q < q_end; ++q)
-              path_body(l1c, l3c, wl + F.w_soff[q], mbuf + F.m_off[q], xl, al);
+              path_body(l1c, std::integral_constant<int, -1>{}, l3c, wl + F.w_soff[q], mbuf + F.m_off[q], xl, al);
           }
         });
       });
@@ -260,6 +285,7 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
         store_vectors<T, CPL, d3>(dst, row);
       }
     });
+  }
   }
   if (!alive) {
     // let copies that are still in flight land before the CTA's shared memory is released
@@ -305,7 +331,12 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
   // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-  const int64_t blocks = grid_blocks(graph->num_edges, edges_per_warp(plan->tuning, 1024), r, dt.sm_count);
+  const double degree = static_cast<double>(graph->num_edges) / static_cast<double>(std::max<int64_t>(graph->num_nodes, 1));
+  const int64_t tile_edges = plan->tuning.fwd_tile_edges > 0 ? plan->tuning.fwd_tile_edges : 96;
+  P.tile_nodes = std::max<int64_t>(1, static_cast<int64_t>(tile_edges / std::max(degree, 1e-3) + 0.5));
+  P.tile_nodes = std::min<int64_t>(P.tile_nodes, 1 << 20);
+  const int64_t num_tiles = ceil_div(std::max<int64_t>(graph->num_nodes, 1), P.tile_nodes);
+  const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(dt.sm_count, ceil_div(num_tiles, nwarps)));
   const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(f.chunks));
   kernel<<<grid, nwarps * 32, block_bytes, stream>>>(P);
   LUNA_LAUNCH_CHECK("staged forward");

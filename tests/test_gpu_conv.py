@@ -221,7 +221,7 @@ def test_input_validation_errors():
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
 @pytest.mark.parametrize("name", ["cfg2", "cfg5", "cfg4"])
 @pytest.mark.parametrize("knob", ["LUNA_B200_NO_CANON=1", "LUNA_B200_NO_SPARSE=1", "LUNA_B200_BWD_KERNEL=row",
-                                  "LUNA_B200_BWD_KERNEL=units", "LUNA_B200_BWD_KERNEL=team"])
+                                  "LUNA_B200_BWD_KERNEL=units", "LUNA_B200_NO_PLAIN=1"])
 def test_staged_kernel_variants_match_oracle(name, dtype, knob, monkeypatch):
     """The canonical configurations through the kernels they do not all take by default: loops over run-time path
     tables (NO_CANON), the unrolled kernel with dense coupling matrices (NO_SPARSE), and the two data-movement
