@@ -37,11 +37,12 @@ from bench_workloads import CUTOFF, DENSITY, WORKLOADS, build_graph_edges, build
 
 # DRAM traffic per edge (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture, divided by the edges of the
 # captured launch), keyed by workload and by the kernel variant that was captured; the summaries under profiles/ give
-# the commands.  The captures ran a smaller graph of the same workload (larger than L2) and traffic grows with the
-# edge count, so the bench scales it to its own launch.  A run whose plan picks another variant reports null.
+# the commands.  The captures are single-pass runs of the two byte counters on this workload at its full size (50,000
+# atoms); a run on another atom count scales them by its edges, which is what the traffic grows with.  A run whose plan
+# picks another variant reports null.
 NCU_TRAFFIC_BYTES_PER_EDGE = {
-    ("cfg2", "forward", "staged"): 11.51e3,
-    ("cfg2", "backward", "row"): 22.32e3,
+    ("cfg2", "forward", "staged"): 10.20e3,
+    ("cfg2", "backward", "row"): 19.50e3,
 }
 SH6_ITEMS = 4_000_000
 # algorithmic FLOPs per edge of the forward pass (sum over paths of channels * (2 * terms + d2))
@@ -421,8 +422,8 @@ class ConvWorkload:
                 "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": peak_kind,
                 "traffic": None if per_edge is None else per_edge * self.edges,
-                "traffic_note": "bytes per launch, scaled by edges from an ncu capture of a smaller case of the same "
-                                "kernel (profiles/)",
+                "traffic_note": "bytes per launch: ncu dram read + write of this kernel on this workload at 50,000 "
+                                "atoms (profiles/), scaled by the edge count",
                 "algorithmic_bytes": dom_bytes,
                 "forward": {"ms": fwd_ms, "GB/s": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "bytes": fwd_bytes},
                 "backward": {"ms": bwd_ms, "GB/s": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "bytes": bwd_bytes},
