@@ -57,12 +57,15 @@ def parse_args():
     p.add_argument("--impl", default="native", choices=["native", "reference"])
     p.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["sh6"])
     p.add_argument("--atoms-per-gpu", type=int, default=None)
-    p.add_argument("--e2e-steps", type=int, default=2)
+    p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--skip-e2e", action="store_true")
     p.add_argument("--skip-cpu", action="store_true")
     p.add_argument("--skip-others", action="store_true")
     p.add_argument("--cpu-seconds", type=float, default=15.0)
     p.add_argument("--generic", action="store_true", help="force the table-driven kernels")
+    p.add_argument("--no-overlap", action="store_true",
+                   help="N > 1: exchange, forward, backward, return one after the other on one stream")
+    p.add_argument("--e2e-chunks", type=int, default=32, help="pieces of the host-streamed step")
     return p.parse_args()
 
 
@@ -320,11 +323,12 @@ def time_steps(step, steps, warmup, marks, world, sampler=None):
 class ConvWorkload:
     """One workload's tensors on this rank, the step that is timed, and its accounting."""
 
-    def __init__(self, name, atoms, world, rank, device, generic=False):
+    def __init__(self, name, atoms, world, rank, device, generic=False, overlap=True):
         import lunaequivariance_b200 as luna
         from lunaequivariance_b200 import sharded
 
         self.name, self.world, self.rank, self.device = name, world, rank, device
+        self.overlap = overlap
         in1, in2, out, instructions, dtype, default_atoms, kind, lmax = build_paths(name)
         self.atoms = atoms or default_atoms
         self.dtype, self.kind, self.lmax = dtype, kind, lmax
@@ -352,6 +356,10 @@ class ConvWorkload:
         from lunaequivariance_b200 import conv as conv_mod
         from lunaequivariance_b200 import sharded
 
+        if self.world > 1 and self.overlap:
+            # the exchanges run on a side stream behind the interior piece of the shard; the intervals are then
+            # "enqueue", "forward pieces incl. any wait for the halo", "backward pieces", "wait + add of the returns"
+            return sharded.overlapped_step(self.op, self.x, self.sh, self.w, self.g, self.shard, events=events)
         mark = (lambda i: events[i].record()) if events is not None else (lambda i: None)
         mark(0)
         x_full = sharded.exchange_halo(self.x, self.shard) if self.world > 1 else self.x
@@ -640,7 +648,8 @@ def main():
             dist.destroy_process_group()
         return
 
-    work = ConvWorkload(args.workload, args.atoms_per_gpu, world, rank, device, args.generic)
+    work = ConvWorkload(args.workload, args.atoms_per_gpu, world, rank, device, args.generic,
+                        overlap=not args.no_overlap)
     result = work.measure(args.steps, args.warmup, sampler)
     clocks = sampler.stop() if sampler else None
     op_status = None
@@ -650,6 +659,8 @@ def main():
         op_status = str(error)
     e2e = None if args.skip_e2e else measure_e2e(args, work, world, device)
     staged, dtype, name = work.op.uses_staged_kernels, work.dtype, work.name
+    lo, hi = work.shard.interior
+    pieces = sum(1 for b, e in ((0, lo), (lo, hi), (hi, work.shard.local_nodes)) if e > b)
     del work
     torch.cuda.empty_cache()
 
@@ -664,7 +675,10 @@ def main():
 
     if rank == 0:
         # kernels of this library per step: forward + backward (+ the harmonics and second-order launches of cfg3)
+        # (a partitioned step with overlap runs forward and backward as up to three pieces each)
         launches_per_step = 9 if name == "cfg3" else (2 if staged else 4)
+        if world > 1 and not args.no_overlap and name != "cfg3":
+            launches_per_step *= pieces
         line = {
             "metric": "uvu_conv_fwd_bwd_edges_per_s", "value": result["value"], "unit": "edges/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": result["ms_per_step"],
@@ -684,11 +698,14 @@ def main():
 
 
 def measure_e2e(args, work, world, device):
-    """Same step through TensorProductConv + autograd with pinned host buffers: H2D of x, edge_attr, weight and
-    the cotangent, D2H of out, gx, gy, gw, every step."""
+    """Same step with the inputs in pinned host memory: H2D of x, edge_attr, weight and the cotangent, D2H of out, gx,
+    gy, gw, every step, through the library's host-streaming executor (``HostStreamedConv``): the per-edge tensors
+    cross PCIe chunk by chunk, uploads, kernels and downloads overlapping.  On a partitioned graph the node features
+    take the usual halo exchange on the device."""
     import torch.distributed as dist
 
     from lunaequivariance_b200 import sharded
+    from lunaequivariance_b200.streaming import HostStreamedConv
 
     module, shard = work.module, work.shard
 
@@ -702,26 +719,25 @@ def measure_e2e(args, work, world, device):
 
     host_in = [pinned(t) for t in (work.x, work.sh, work.w, work.g)]
     E = work.edges
-    out_shapes = [(work.atoms, module.op.out_dim), tuple(work.x.shape), tuple(work.sh.shape), tuple(work.w.shape)]
-    try:
-        host_out = [torch.empty(s, dtype=work.dtype, pin_memory=True) for s in out_shapes]
-    except RuntimeError:
-        host_out = [torch.empty(s, dtype=work.dtype) for s in out_shapes]
+    streamed = HostStreamedConv(module.op, shard.graph, chunks=args.e2e_chunks)
+    host_gx = pinned(work.x)
     h2d = sum(t.numel() * t.element_size() for t in host_in)
-    d2h = sum(t.numel() * t.element_size() for t in host_out)
     work.w = work.g = None  # the step owns its device copies
     torch.cuda.empty_cache()
+    d2h = 0
 
     def one():
-        xd, yd, wd, gd = (t.to(device, non_blocking=True) for t in host_in)
-        xd.requires_grad_(True)
-        yd.requires_grad_(True)
-        wd.requires_grad_(True)
-        result = sharded.sharded_conv(module, xd, yd, wd, shard) if world > 1 else module(xd, yd, wd, graph=shard.graph)
-        grads = torch.autograd.grad(result, (xd, yd, wd), gd)
-        for host, dev in zip(host_out, (result.detach(), *grads)):
-            host.copy_(dev, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        nonlocal d2h
+        x_host, y_host, w_host, g_host = host_in
+        if world > 1:
+            x_full = sharded.exchange_halo(x_host.to(device, non_blocking=True), shard)
+            out, gx_full, gy, gw = streamed.step(x_full, y_host, w_host, g_host)
+            host_gx.copy_(sharded.return_halo(gx_full, shard), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            gx = host_gx
+        else:
+            out, gx, gy, gw = streamed.step(x_host, y_host, w_host, g_host)
+        d2h = sum(t.numel() * t.element_size() for t in (out, gx, gy, gw))
 
     one()
     torch.cuda.synchronize()
@@ -738,7 +754,8 @@ def measure_e2e(args, work, world, device):
         dist.all_reduce(edges, op=dist.ReduceOp.SUM)
     return {"value": edges.item() * args.e2e_steps / elapsed.item(), "unit": "edges/s",
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
-            "pinned": bool(host_in[2].is_pinned())}
+            "pinned": bool(host_in[2].is_pinned()), "api": "HostStreamedConv.step",
+            "chunks": len(streamed.pieces)}
 
 
 if __name__ == "__main__":

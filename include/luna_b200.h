@@ -136,6 +136,16 @@ LUNA_API int luna_uvu_conv_bwd(luna_uvu_plan* plan, const luna_graph* graph, con
                       const void* g, void* gx, void* gy, void* gw, void* scratch, int64_t scratch_bytes,
                       void* stream);
 
+/* As luna_uvu_conv_bwd, except that gx is added to instead of written: gx[s] += dF/dx[s], and rows of sources without
+ * an edge in this graph are left alone.  gy and gw are written as usual.  For callers that cut one graph's
+ * destination-sorted edge list into several calls (destination sub-ranges): each call gets the slice of y, w, gy, gw
+ * of its edges by pointer offset, and the calls add up the gradient of the shared source rows.  Used here to overlap
+ * a halo exchange with the interior of a shard and to stream per-edge tensors from host memory chunk by chunk.  No
+ * counterpart in the reference, whose backward always covers the whole graph (backward.py:572-681). */
+LUNA_API int luna_uvu_conv_bwd_add_gx(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,
+                             const void* w, const void* g, void* gx, void* gy, void* gw, void* scratch,
+                             int64_t scratch_bytes, void* stream);
+
 /* Same result as luna_uvu_conv_bwd, for callers that cannot allocate device memory and so have no scratch
  * buffer to pass: code running inside another program's step without an allocator of its own, loops that must
  * not hit cudaMalloc's device-wide synchronisation, processes whose memory pool is fixed at start-up.  No

@@ -89,6 +89,8 @@ _SIGNATURES = {
     "luna_uvu_conv_fwd": (ctypes.c_int, [_P, ctypes.POINTER(Graph), _P, _P, _P, _P, _P]),
     "luna_uvu_conv_bwd": (ctypes.c_int, [_P, ctypes.POINTER(Graph), _P, _P, _P, _P, _P, _P, _P, _P,
                                          ctypes.c_int64, _P]),
+    "luna_uvu_conv_bwd_add_gx": (ctypes.c_int, [_P, ctypes.POINTER(Graph), _P, _P, _P, _P, _P, _P, _P, _P,
+                                                ctypes.c_int64, _P]),
     "luna_uvu_conv_noalloc_max_scratch_bytes": (ctypes.c_int64, []),
     "luna_uvu_conv_noalloc_prepare": (ctypes.c_int, [_P]),
     "luna_uvu_conv_bwd_noalloc": (ctypes.c_int, [_P, ctypes.POINTER(Graph), _P, _P, _P, _P, _P, _P, _P, _P]),

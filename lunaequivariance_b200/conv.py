@@ -330,11 +330,23 @@ def _graph_struct(graph):
     return graph.struct, graph.num_nodes, graph.source_rows, graph.num_edges
 
 
-def run_forward(op: LunaTPUVUConv, x, y, w, graph) -> torch.Tensor:
+def _output(given, shape, like: torch.Tensor, name: str) -> torch.Tensor:
+    """A caller-supplied output tensor (checked) or a fresh one."""
+    if given is None:
+        return torch.empty(shape, dtype=like.dtype, device=like.device)
+    if tuple(given.shape) != tuple(shape) or given.dtype != like.dtype or given.device != like.device:
+        raise ValueError(f"{name} must be a {like.dtype} tensor of shape {tuple(shape)} on {like.device}")
+    if not given.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return given
+
+
+def run_forward(op: LunaTPUVUConv, x, y, w, graph, *, out=None) -> torch.Tensor:
+    """``out`` may name the tensor to write (for example a row range of a larger one)."""
     struct, n, ns, e = _graph_struct(graph)
     _check_inputs(op, x, y, w, ns, e)
     x, y, w = _prepared(x), _prepared(y), _prepared(w)
-    out = torch.empty((n, op.out_dim), dtype=x.dtype, device=x.device)
+    out = _output(out, (n, op.out_dim), x, "out")
     with torch.cuda.device(x.device):
         _native.check(_native.library().luna_uvu_conv_fwd(
             op._plan.handle, ctypes.byref(struct), x.data_ptr(), y.data_ptr(), w.data_ptr(), out.data_ptr(),
@@ -342,20 +354,26 @@ def run_forward(op: LunaTPUVUConv, x, y, w, graph) -> torch.Tensor:
     return out
 
 
-def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True)):
+def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True), *, out=(None, None, None),
+                 add_gx=False):
+    """``out`` may name the tensors to write (gx, gy, gw; each optional).  With ``add_gx`` the source-row gradient
+    is added to ``out[0]`` instead of written: calls on pieces of one graph's edge list then sum up to the whole."""
     struct, n, ns, e = _graph_struct(graph)
     _check_inputs(op, x, y, w, ns, e, g=g, num_nodes=n)
     x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
     if not any(needs):
         return None, None, None
-    gx = torch.empty_like(x) if needs[0] else None
-    gy = torch.empty_like(y) if needs[1] else None
-    gw = torch.empty_like(w) if needs[2] else None
+    if add_gx and (not needs[0] or out[0] is None):
+        raise ValueError("add_gx needs the tensor to add to as out[0]")
+    gx = _output(out[0], x.shape, x, "gx") if needs[0] else None
+    gy = _output(out[1], y.shape, y, "gy") if needs[1] else None
+    gw = _output(out[2], w.shape, w, "gw") if needs[2] else None
     if e == 0 or n == 0:
-        return tuple(None if t is None else t.zero_() for t in (gx, gy, gw))
+        return tuple(None if t is None else (t if add_gx and t is gx else t.zero_()) for t in (gx, gy, gw))
+    entry = _native.library().luna_uvu_conv_bwd_add_gx if add_gx else _native.library().luna_uvu_conv_bwd
     with torch.cuda.device(x.device):
         scratch, size = _scratch(op, n, e, x.device)
-        _native.check(_native.library().luna_uvu_conv_bwd(
+        _native.check(entry(
             op._plan.handle, ctypes.byref(struct), x.data_ptr(), y.data_ptr(), w.data_ptr(), g.data_ptr(),
             _native.pointer(gx), _native.pointer(gy), _native.pointer(gw), _native.pointer(scratch), size,
             _native.current_stream(x.device)))

@@ -92,9 +92,10 @@ extern "C" int luna_uvu_conv_fwd(luna_uvu_plan* plan, const luna_graph* graph, c
   return generic_contract(plan, graph, kFreeG, x, y, w, nullptr, out, false, stream);
 }
 
-extern "C" int luna_uvu_conv_bwd(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,
-                                 const void* w, const void* g, void* gx, void* gy, void* gw, void* scratch,
-                                 int64_t scratch_bytes, void* stream_) {
+namespace {
+int backward_entry(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y, const void* w,
+                   const void* g, void* gx, bool add_gx, void* gy, void* gw, void* scratch, int64_t scratch_bytes,
+                   void* stream_) {
   clear_error();
   auto stream = static_cast<cudaStream_t>(stream_);
   LUNA_TRY(check_common(plan, graph));
@@ -106,13 +107,26 @@ extern "C" int luna_uvu_conv_bwd(luna_uvu_plan* plan, const luna_graph* graph, c
   LUNA_TRY(check_ptr(plan, gx, "gx", false, 0));
   LUNA_TRY(check_ptr(plan, gy, "gy", false, 0));
   LUNA_TRY(check_ptr(plan, gw, "gw", false, 0));
-  if (E == 0 || N == 0) return zero_fill(gx, src_rows(graph) * plan->X, elem_size(plan), stream);
+  if (E == 0 || N == 0) return add_gx ? LUNA_OK : zero_fill(gx, src_rows(graph) * plan->X, elem_size(plan), stream);
   if (use_fast(plan, {x, w, g, gx, gw}))
-    return fast_backward(plan, graph, x, y, w, g, gx, false, gy, false, gw, false, scratch, scratch_bytes, stream);
-  if (gx) LUNA_TRY(generic_contract(plan, graph, kFreeX, nullptr, y, w, g, gx, false, stream));
+    return fast_backward(plan, graph, x, y, w, g, gx, add_gx, gy, false, gw, false, scratch, scratch_bytes, stream);
+  if (gx) LUNA_TRY(generic_contract(plan, graph, kFreeX, nullptr, y, w, g, gx, add_gx, stream));
   if (gy) LUNA_TRY(generic_contract(plan, graph, kFreeY, x, nullptr, w, g, gy, false, stream));
   if (gw) LUNA_TRY(generic_contract(plan, graph, kFreeW, x, y, nullptr, g, gw, false, stream));
   return LUNA_OK;
+}
+}  // namespace
+
+extern "C" int luna_uvu_conv_bwd(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,
+                                 const void* w, const void* g, void* gx, void* gy, void* gw, void* scratch,
+                                 int64_t scratch_bytes, void* stream) {
+  return backward_entry(plan, graph, x, y, w, g, gx, false, gy, gw, scratch, scratch_bytes, stream);
+}
+
+extern "C" int luna_uvu_conv_bwd_add_gx(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,
+                                        const void* w, const void* g, void* gx, void* gy, void* gw, void* scratch,
+                                        int64_t scratch_bytes, void* stream) {
+  return backward_entry(plan, graph, x, y, w, g, gx, true, gy, gw, scratch, scratch_bytes, stream);
 }
 
 extern "C" int luna_uvu_conv_dbl_bwd(luna_uvu_plan* plan, const luna_graph* graph, const void* x, const void* y,

@@ -372,6 +372,8 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   };
   int zero = 0;
   const size_t o_status = append(&zero, sizeof(int));
+  const std::vector<unsigned> no_counts(static_cast<size_t>(kTileCounterSets) * kTileCounterWords, 0u);
+  const size_t o_counters = append(no_counts.data(), no_counts.size() * sizeof(unsigned));
   const size_t o_paths = append(plan->paths.data(), plan->paths.size() * sizeof(PathRec));
   const size_t o_os = append(plan->out_slots.data(), plan->out_slots.size() * sizeof(SlotRec));
   const size_t o_xs = append(plan->x_slots.data(), plan->x_slots.size() * sizeof(SlotRec));
@@ -440,6 +442,7 @@ int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out) {
   }
   auto* base = static_cast<unsigned char*>(dt.buffer);
   dt.status = reinterpret_cast<int*>(base + o_status);
+  dt.tile_counters = reinterpret_cast<unsigned*>(base + o_counters);
   dt.paths = reinterpret_cast<const PathRec*>(base + o_paths);
   dt.out_slots = reinterpret_cast<const SlotRec*>(base + o_os);
   dt.x_slots = reinterpret_cast<const SlotRec*>(base + o_xs);

@@ -4,6 +4,7 @@
 #include <array>
 #include <cstdint>
 #include <map>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -122,10 +123,17 @@ struct Tuning {
 };
 Tuning tuning_from_environment();
 
+constexpr int kTileCounterSets = 32;    // launches of one plan that may be in flight on a device at a time
+constexpr int kTileCounterWords = 16;   // per set: (next tile, warps finished) for up to 8 channel chunks
+
 struct DeviceTables {
   void* buffer = nullptr;  // one allocation holding every table
   size_t bytes = 0;
   int* status = nullptr;   // device status word (inside buffer)
+  // Work counters of the kernels that hand out tiles of nodes dynamically: kTileCounterSets sets of
+  // kTileCounterWords zero-initialised words (inside buffer).  A launch takes the next set in turn; its last warp
+  // to finish puts the set back to zero, so no launch has to clear anything.
+  unsigned* tile_counters = nullptr;
   // resolved pointers (type-erased; reinterpret for the plan's dtype)
   const PathRec* paths = nullptr;
   const SlotRec *out_slots = nullptr, *x_slots = nullptr, *y_slots = nullptr;
@@ -177,12 +185,19 @@ struct luna_uvu_plan {
 
   std::mutex mutex;
   std::map<int, luna::DeviceTables> device_tables;
+  mutable std::atomic<unsigned> tile_counter_cursor{0};
 };
 
 namespace luna {
 
 // Returns the tables for the current device, uploading them on first use.
 int get_device_tables(luna_uvu_plan* plan, const DeviceTables** out);
+
+// The set of tile counters for the next launch of this plan on the device of `dt`.
+inline unsigned* next_tile_counters(const luna_uvu_plan* plan, const DeviceTables& dt) {
+  const unsigned set = plan->tile_counter_cursor.fetch_add(1u, std::memory_order_relaxed) % kTileCounterSets;
+  return dt.tile_counters + static_cast<size_t>(set) * kTileCounterWords;
+}
 
 template <typename T>
 GenericTables<T> generic_tables(const luna_uvu_plan* plan, const DeviceTables& dt) {

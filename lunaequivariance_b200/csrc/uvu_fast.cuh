@@ -219,6 +219,27 @@ Residency choose_residency(size_t ring_bytes, size_t fixed_bytes, size_t shared_
 int64_t grid_blocks(int64_t num_edges, int64_t target, const Residency& r, int sm_count);
 
 // Target edges per warp when sizing the grid: the plan's override if it has one.
+#ifdef __CUDACC__
+// Dynamic hand-out of tiles to warps.  counters[0] counts tiles taken beyond every warp's first one, counters[1] the
+// warps that are done; the last warp out clears both for the next launch that gets this set.
+__device__ __forceinline__ int64_t take_tile(unsigned* counters, int64_t total_warps, int lane) {
+  unsigned ticket = 0;
+  if (lane == 0) ticket = atomicAdd(&counters[0], 1u);
+  ticket = __shfl_sync(0xffffffffu, ticket, 0);
+  return total_warps + static_cast<int64_t>(ticket);
+}
+__device__ __forceinline__ void leave_tiles(unsigned* counters, int64_t total_warps, int lane) {
+  if (lane == 0) {
+    const unsigned done = atomicAdd(&counters[1], 1u);
+    if (static_cast<int64_t>(done) + 1 == total_warps) {  // every other warp has taken its last ticket
+      counters[0] = 0u;
+      counters[1] = 0u;
+      __threadfence();
+    }
+  }
+}
+#endif
+
 inline int64_t edges_per_warp(const Tuning& tuning, int64_t fallback) {
   return tuning.edges_per_warp > 0 ? tuning.edges_per_warp : fallback;
 }

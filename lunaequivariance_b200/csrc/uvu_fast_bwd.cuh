@@ -582,9 +582,9 @@ int launch_fast_bwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
     // compiled-in coupling patterns, if the plan's terms have them
     if constexpr (sparse_shape_ok<LX, (L2 < 0 ? 0 : L2), LO>()) {
       const int variant = fast_bwd_variant(plan);
-      // The call training makes all the time - every gradient, nothing accumulated, one warp pass per block - has
-      // kernels with a compile-time layout.
-      const bool plain = gx != nullptr && gy != nullptr && gw != nullptr && !acc_x && !acc_y && !acc_w &&
+      // The call training makes all the time - every gradient, gy and gw not accumulated, one warp pass per block -
+      // has kernels with a compile-time layout.
+      const bool plain = gx != nullptr && gy != nullptr && gw != nullptr && !acc_y && !acc_w &&
                          f.chunks == 1 && variant == LUNA_BWD_ROW_STAGES && !plan->tuning.no_plain;
       if (plain) {
         const int rc = launch_fast_bwd_plain_any<T, CPL>(plan, dt, graph, P, stream);

@@ -1,6 +1,6 @@
 // First-derivative kernel for the case training runs all the time: a canonical path list with compiled-in coupling
-// patterns, one warp pass covers the channels of a block (channels == 32 * CPL), all three gradients wanted, nothing
-// accumulated.  Everything about the layout is then a compile-time constant - row lengths, block offsets, which
+// patterns, one warp pass covers the channels of a block (channels == 32 * CPL), all three gradients wanted, gy and gw
+// not accumulated (gx may be: callers that split a graph's edges over several calls add the pieces up).  Everything about the layout is then a compile-time constant - row lengths, block offsets, which
 // paths exist - so the kernel carries no layout tables, tests no output flags and computes no addresses from them.
 //
 // One warp per edge.  Two ways of splitting an edge between two warps were measured on the 128-channel
@@ -16,8 +16,9 @@
 // a byte count) signal arrivals; every wait is bounded, and a wait that runs out sets the plan's status word and ends
 // the warp's loop.
 //
-// Work assignment.  Source nodes are cut into small tiles of consecutive nodes; warp q of Q takes tiles q, q + Q, ...
-// All resident warps therefore work on neighbouring source nodes at any moment, and for a spatially ordered graph the
+// Work assignment.  Source nodes are cut into small tiles of consecutive nodes, handed out in ascending order: a
+// warp's first tile is its own number, further ones come from a counter (take_tile), so a warp that started late
+// takes fewer.  All resident warps work on neighbouring source nodes at any moment, and for a spatially ordered graph the
 // g[dst] rows they gather are the same few thousand rows, which stay in L2.  gx of a node is accumulated in registers
 // by the one warp that owns the node: no atomics, results do not depend on the assignment.
 #pragma once
@@ -48,7 +49,9 @@ struct PlainParams {
   int* status;
   int64_t num_src_nodes;
   int64_t tile_nodes;
+  unsigned* tile_counters;     // (next tile, warps finished)
   int slots, row_stages;
+  int acc_x;                   // gx += instead of gx =
   int two;                     // always 2: source of the run-time 1.0 that settles freshly assembled pairs
 };
 
@@ -162,8 +165,10 @@ __device__ __forceinline__ void plain_loop(const PlainParams<T>& P, const PlainM
   const int64_t tile_nodes = P.tile_nodes;
   const int64_t num_tiles = (N + tile_nodes - 1) / tile_nodes;
 
+  int64_t tile = first_tile, tile_after = first_tile;
 #pragma unroll 1
-  for (int64_t tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
+  for (; tile < num_tiles && alive; tile = tile_after) {
+    tile_after = take_tile(P.tile_counters, tile_step, lane);  // one ahead of need
     const int64_t n_lo = tile * tile_nodes;
     const int64_t n_hi = n_lo + tile_nodes < N ? n_lo + tile_nodes : N;
     const int64_t p_begin = P.src_rowptr[n_lo], p_end = P.src_rowptr[n_hi];
@@ -324,10 +329,18 @@ __device__ __forceinline__ void plain_loop(const PlainParams<T>& P, const PlainM
         constexpr int d1 = 2 * l1 + 1;
         T row[CPL * d1];  // memory order: channel-major, component-minor
         unpack_packets<PK, T, CPL, d1>(&gxr[l1 * l1 * NP], row);
-        store_vectors<T, CPL, d1>(P.gx + n * X + ch * l1 * l1 + lane * (CPL * d1), row);
+        T* to = P.gx + n * X + ch * l1 * l1 + lane * (CPL * d1);
+        if (P.acc_x) {
+          T old[CPL * d1];
+          load_vectors<T, CPL, d1>(to, old);
+#pragma unroll
+          for (int a = 0; a < CPL * d1; ++a) row[a] += old[a];
+        }
+        store_vectors<T, CPL, d1>(to, row);
       });
     }
   }
+  leave_tiles(P.tile_counters, tile_step, lane);
   if (lane == 0) bulk_wait_group_read_all();
   if (!alive) {  // let copies that are still in flight land as well (bounded)
     for (int v = 0; v < R; ++v) mbar_wait_bounded(&M.gfull[v], (gfull_par >> v) & 1u);
@@ -406,6 +419,8 @@ int launch_fast_bwd_plain(const luna_uvu_plan* plan, const DeviceTables& dt, con
   P.sp_j = dt.sp_j;
   P.status = B.status;
   P.num_src_nodes = B.num_src_nodes;
+  P.acc_x = B.acc_x ? 1 : 0;
+  P.tile_counters = next_tile_counters(plan, dt);
   P.two = 2;
   auto kernel = fast_bwd_plain_kernel<T, CPL, LX, L2, LO>;
   cudaFuncAttributes attr;

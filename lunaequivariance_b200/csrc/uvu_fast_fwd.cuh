@@ -1,8 +1,9 @@
 // Staged forward-shaped kernel (free argument g):  out[t] = sum_{e: dst e = t} sum_p w_p * (M^p(y_e)^T x[src e]).
 //
-// Destination nodes are cut into small tiles of consecutive nodes, and warp q of Q takes tiles q, q + Q, ...: a tile
-// is a contiguous piece of the destination-sorted edge list, reduced by one warp with register accumulators and no
-// atomics, and at any moment the resident warps work on neighbouring destination nodes, so that for a spatially
+// Destination nodes are cut into small tiles of consecutive nodes, handed to the warps in ascending order (the first
+// round statically, then from a counter): a tile is a contiguous piece of the destination-sorted edge list, reduced
+// by one warp with register accumulators and no atomics on data (results do not depend on which warp took a tile),
+// and at any moment the resident warps work on neighbouring destination nodes, so that for a spatially
 // ordered graph the x[src] rows they gather are the same few thousand rows and stay in L2.  Per
 // edge, lanes issue 1-D bulk copies (cp.async.bulk, completion on an mbarrier) of the edge's weight row and of the
 // gathered x[src] row into the warp's ring of shared-memory stages; the warp then reads them with 128-bit shared
@@ -54,6 +55,7 @@ struct FwdParams {
   int* status;
   int64_t num_nodes, num_edges;
   int64_t tile_nodes;  // destination nodes per tile
+  unsigned* tile_counters;  // (next tile, warps finished) per channel chunk
   int stages;
   int accumulate;
 };
@@ -184,8 +186,13 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
     });
   };
 
+  // A warp's first tile is its own number; further tiles are taken from a counter, one ahead of need, so that a warp
+  // that started late or met long rows simply takes fewer.
+  unsigned* counters = P.tile_counters + 2 * blockIdx.y;
+  int64_t tile = gwarp;
 #pragma unroll 1
-  for (int64_t tile = gwarp; tile < num_tiles && alive; tile += total_warps) {
+  while (tile < num_tiles && alive) {
+  const int64_t tile_after = take_tile(counters, total_warps, lane);
   const int64_t n_lo = tile * P.tile_nodes;
   const int64_t n_hi = n_lo + P.tile_nodes < N ? n_lo + P.tile_nodes : N;
   const int64_t e_begin = P.dst_rowptr[n_lo];
@@ -286,7 +293,9 @@ __global__ void __launch_bounds__(kFwdMaxWarps * 32, 1) fast_fwd_kernel(const __
       }
     });
   }
+  tile = tile_after;
   }
+  leave_tiles(counters, total_warps, lane);
   if (!alive) {
     // let copies that are still in flight land before the CTA's shared memory is released
     for (int d = 1; d < stages; ++d) {
@@ -318,6 +327,7 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   P.num_nodes = graph->num_nodes;
   P.num_edges = graph->num_edges;
   P.accumulate = accumulate ? 1 : 0;
+  P.tile_counters = next_tile_counters(plan, dt);
   const size_t stage = static_cast<size_t>(f.w_stage_elems + f.x_stage_elems) * sizeof(T);
   auto kernel = fast_fwd_kernel<T, CPL, LX, LO, L2>;
   cudaFuncAttributes attr;

@@ -70,6 +70,25 @@ class LunaTPGraph:
             self._tables["native"] = view
         return view
 
+    def destination_range(self, begin: int, end: int) -> "tuple[LunaTPGraph, int, int]":
+        """The graph of the edges whose destination lies in ``[begin, end)``, and that slice ``[e0, e1)`` of the edge
+        list: destinations renumbered from zero, sources as they are.
+
+        Because edges are sorted by destination the slice is contiguous, so per-edge tensors of the piece are row
+        ranges of the whole graph's (``y[e0:e1]``, ``w[e0:e1]``) and its output rows are ``out[begin:end]``.  Pieces
+        that tile ``[0, num_nodes)`` together do the work of the whole graph; only the source-row gradients of the
+        pieces have to be added up.  No counterpart in the reference.  Cached per range.
+        """
+        if not 0 <= begin <= end <= self.num_nodes:
+            raise ValueError(f"destination range [{begin}, {end}) outside [0, {self.num_nodes}]")
+        key = ("range", int(begin), int(end))
+        cached = self._tables.get(key)
+        if cached is None:
+            e0, e1 = (int(v) for v in self.dst_rowptr[[begin, end]].tolist())
+            piece = make_graph(self.src[e0:e1], self.dst[e0:e1] - begin, end - begin, num_src_nodes=self.source_rows)
+            cached = self._tables[key] = (piece, e0, e1)
+        return cached
+
     def table_list(self) -> list:
         """The 13 tensors the reference passes to its custom ops (``src/lunatp/uvu_conv/interface.py:186-192``)."""
         seg = self.source_segments

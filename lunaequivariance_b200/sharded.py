@@ -39,6 +39,7 @@ class GraphShard:
     send_counts: tuple        # owned rows each rank wants from this one
     send_rows: torch.Tensor   # local indices of those rows, grouped by requesting rank
     group: object = None
+    interior: tuple = (0, 0)  # longest run [begin, end) of local destinations all of whose sources are owned
 
     @property
     def local_nodes(self) -> int:
@@ -79,7 +80,9 @@ def make_graph_shard(src_global: torch.Tensor, dst_global: torch.Tensor, node_co
     owned = (src64 >= begin) & (src64 < begin + local)
     halo_ids = torch.unique(src64[~owned])  # sorted ascending
     compact = torch.where(owned, src64 - begin, local + torch.searchsorted(halo_ids, src64))
-    graph = make_graph(compact, dst_global.to(torch.int64) - begin, local, num_src_nodes=local + halo_ids.numel())
+    dst_local = dst_global.to(torch.int64) - begin
+    graph = make_graph(compact, dst_local, local, num_src_nodes=local + halo_ids.numel())
+    interior = _longest_interior_run(torch.unique(dst_local[~owned]), local)
 
     bounds = _bounds(node_counts, device)
     owner = torch.searchsorted(bounds, halo_ids, right=True) - 1
@@ -98,7 +101,22 @@ def make_graph_shard(src_global: torch.Tensor, dst_global: torch.Tensor, node_co
         recv_list, send_list = recv_counts.tolist(), [0] * world
         send_rows = torch.empty(0, dtype=torch.int64, device=device)
     return GraphShard(graph=graph, node_begin=begin, node_counts=node_counts, halo_ids=halo_ids,
-                      recv_counts=tuple(recv_list), send_counts=tuple(send_list), send_rows=send_rows, group=group)
+                      recv_counts=tuple(recv_list), send_counts=tuple(send_list), send_rows=send_rows, group=group,
+                      interior=interior)
+
+
+def _longest_interior_run(boundary_nodes: torch.Tensor, local: int) -> tuple:
+    """``boundary_nodes``: ascending local ids of the destinations that read a remote source.  Returns the longest
+    run of consecutive destinations between them."""
+    if local == 0:
+        return (0, 0)
+    if boundary_nodes.numel() == 0:
+        return (0, local)
+    fence = torch.cat([boundary_nodes.new_tensor([-1]), boundary_nodes, boundary_nodes.new_tensor([local])])
+    gaps = fence[1:] - fence[:-1] - 1
+    where = int(torch.argmax(gaps))
+    start = int(fence[where]) + 1
+    return (start, start + int(gaps[where]))
 
 
 def exchange_halo(x_local: torch.Tensor, shard: GraphShard) -> torch.Tensor:
@@ -178,6 +196,110 @@ def sharded_conv(conv, x_local: torch.Tensor, edge_attr: torch.Tensor, weight: t
     return conv(gather_sources(x_local, shard), edge_attr, weight, graph=shard.graph)
 
 
+_side_streams: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(key)
+    return _side_streams[key]
+
+
+def overlapped_step(op, x_local: torch.Tensor, edge_attr: torch.Tensor, weight: torch.Tensor,
+                    grad_out: torch.Tensor, shard: GraphShard, *, halo_rows: torch.Tensor | None = None,
+                    events=None):
+    """Forward and first derivatives on this rank's shard with both halo exchanges hidden behind kernels.
+
+    The destinations of a shard whose sources are all owned form (for a spatially ordered partition) one long
+    interior run; the rest sit at the two ends of the range.  The three runs are three pieces of the
+    destination-sorted edge list (``LunaTPGraph.destination_range``), so:
+
+    * forward: the ``x`` halo travels on a side stream while the interior piece runs; the two end pieces follow;
+    * backward: the end pieces run first - they alone produce gradient rows for the halo - then those rows travel
+      back while the interior piece runs, and are added to the owned rows at the end (one peer after the other, as
+      in ``return_halo``).
+
+    Returns ``(out, gx_local, gy, gw)`` for the owned rows and the rank's edges; the values are those of
+    ``exchange_halo`` + one forward + one backward + ``return_halo``.  ``op`` is the prepared operator
+    (``TensorProductConv(...).op``).  ``halo_rows`` replaces the forward exchange with rows the caller already has
+    and skips the return exchange (``gx`` then has the compact buffer's rows): this is how one rank of a partition
+    is checked on a single GPU.  ``events``: optional five CUDA events recorded at start, after the forward
+    exchange was enqueued, after the forward pieces, after the backward pieces, at the end.
+    """
+    from .conv import run_backward, run_forward
+
+    graph, local, halo = shard.graph, shard.local_nodes, shard.halo_rows
+    lo, hi = shard.interior
+    exchange = halo_rows is None and shard.world_size > 1
+    main = torch.cuda.current_stream(x_local.device)
+    side = _side_stream(x_local.device)
+    mark = (lambda i: events[i].record(main)) if events is not None else (lambda i: None)
+    pieces = [(b, e, *graph.destination_range(b, e)) for b, e in ((0, lo), (hi, local), (lo, hi)) if e > b]
+    ends, inner = [p for p in pieces if (p[0], p[1]) != (lo, hi)], [p for p in pieces if (p[0], p[1]) == (lo, hi)]
+
+    mark(0)
+    full = x_local.new_empty((local + halo, *x_local.shape[1:]))
+    full[:local] = x_local
+    arrived = torch.cuda.Event()
+    if exchange:
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            outgoing = x_local.index_select(0, shard.send_rows)
+            dist.all_to_all_single(full[local:], outgoing, output_split_sizes=list(shard.recv_counts),
+                                   input_split_sizes=list(shard.send_counts), group=shard.group)
+            arrived.record(side)
+            outgoing.record_stream(side)
+    elif halo:
+        full[local:] = halo_rows
+    mark(1)
+    out = x_local.new_empty((local, op.out_dim))
+    for begin, end, piece, e0, e1 in inner:  # reads owned rows only
+        run_forward(op, full, edge_attr[e0:e1], weight[e0:e1], piece, out=out[begin:end])
+    if exchange:
+        main.wait_event(arrived)
+    for begin, end, piece, e0, e1 in ends:
+        run_forward(op, full, edge_attr[e0:e1], weight[e0:e1], piece, out=out[begin:end])
+    mark(2)
+
+    gx_full = torch.zeros_like(full)
+    gy, gw = torch.empty_like(edge_attr), torch.empty_like(weight)
+
+    def backward_piece(begin, end, piece, e0, e1):
+        run_backward(op, full, edge_attr[e0:e1], weight[e0:e1], grad_out[begin:end], piece,
+                     out=(gx_full, gy[e0:e1], gw[e0:e1]), add_gx=True)
+
+    for item in ends:
+        backward_piece(*item)
+    incoming, returned = None, torch.cuda.Event()
+    if exchange:
+        produced = torch.cuda.Event()
+        produced.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(produced)
+            incoming = gx_full.new_empty((sum(shard.send_counts), *gx_full.shape[1:]))
+            dist.all_to_all_single(incoming, gx_full[local:], output_split_sizes=list(shard.send_counts),
+                                   input_split_sizes=list(shard.recv_counts), group=shard.group)
+            returned.record(side)
+    for item in inner:  # adds to owned rows only
+        backward_piece(*item)
+    mark(3)
+    if not exchange:
+        mark(4)
+        return out, (gx_full if halo_rows is not None else gx_full[:local]), gy, gw
+    main.wait_event(returned)
+    incoming.record_stream(main)
+    own, offset = gx_full[:local], 0
+    for count in shard.send_counts:
+        if count:
+            own.index_add_(0, shard.send_rows[offset:offset + count], incoming[offset:offset + count])
+            offset += count
+    mark(4)
+    return out, own, gy, gw
+
+
 def balanced_node_ranges(dst_rowptr: torch.Tensor, parts: int) -> list[tuple[int, int]]:
     """Contiguous destination ranges with near-equal edge counts (row-pointer search, not node counts)."""
     rowptr = dst_rowptr.to("cpu", torch.int64)
@@ -190,4 +312,4 @@ def balanced_node_ranges(dst_rowptr: torch.Tensor, parts: int) -> list[tuple[int
 
 
 __all__ = ["GraphShard", "make_graph_shard", "gather_sources", "scatter_source_gradients", "exchange_halo",
-           "return_halo", "sharded_conv", "balanced_node_ranges"]
+           "return_halo", "sharded_conv", "overlapped_step", "balanced_node_ranges"]
