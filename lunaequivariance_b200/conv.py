@@ -341,8 +341,25 @@ def _output(given, shape, like: torch.Tensor, name: str) -> torch.Tensor:
     return given
 
 
+def _split_of(graph):
+    """The virtual-row form of a graph with very long rows (``LunaTPGraph.split_rows``), else ``None``."""
+    return graph.split_rows() if isinstance(graph, LunaTPGraph) else None
+
+
+def _deliver(value, given, add=False):
+    """Hand a computed tensor over in the caller's tensor, if there is one."""
+    if given is None or value is None:
+        return value
+    return given.add_(value) if add else given.copy_(value)
+
+
 def run_forward(op: LunaTPUVUConv, x, y, w, graph, *, out=None) -> torch.Tensor:
     """``out`` may name the tensor to write (for example a row range of a larger one)."""
+    split = _split_of(graph)
+    if split is not None:  # long rows are walked as several virtual rows, then summed
+        _check_inputs(op, x, y, w, graph.source_rows, graph.num_edges)
+        virtual = run_forward(op, split.sources.gather(x), y, w, split.graph)
+        return _deliver(split.destinations.reduce(virtual), out)
     struct, n, ns, e = _graph_struct(graph)
     _check_inputs(op, x, y, w, ns, e)
     x, y, w = _prepared(x), _prepared(y), _prepared(w)
@@ -358,13 +375,19 @@ def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True),
                  add_gx=False):
     """``out`` may name the tensors to write (gx, gy, gw; each optional).  With ``add_gx`` the source-row gradient
     is added to ``out[0]`` instead of written: calls on pieces of one graph's edge list then sum up to the whole."""
+    if add_gx and (not needs[0] or out[0] is None):
+        raise ValueError("add_gx needs the tensor to add to as out[0]")
+    split = _split_of(graph)
+    if split is not None:
+        _check_inputs(op, x, y, w, graph.source_rows, graph.num_edges, g=g, num_nodes=graph.num_nodes)
+        gx, gy, gw = run_backward(op, split.sources.gather(x), y, w, split.destinations.gather(g), split.graph,
+                                  needs, out=(None, out[1], out[2]))
+        return _deliver(split.sources.reduce(gx), out[0], add_gx), gy, gw
     struct, n, ns, e = _graph_struct(graph)
     _check_inputs(op, x, y, w, ns, e, g=g, num_nodes=n)
     x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)
     if not any(needs):
         return None, None, None
-    if add_gx and (not needs[0] or out[0] is None):
-        raise ValueError("add_gx needs the tensor to add to as out[0]")
     gx = _output(out[0], x.shape, x, "gx") if needs[0] else None
     gy = _output(out[1], y.shape, y, "gy") if needs[1] else None
     gw = _output(out[2], w.shape, w, "gw") if needs[2] else None
@@ -381,6 +404,14 @@ def run_backward(op: LunaTPUVUConv, x, y, w, g, graph, needs=(True, True, True),
 
 
 def run_double_backward(op: LunaTPUVUConv, x, y, w, g, rx, ry, rw, graph, needs=(True, True, True, True)):
+    split = _split_of(graph)
+    if split is not None:
+        _check_inputs(op, x, y, w, graph.source_rows, graph.num_edges, g=g, num_nodes=graph.num_nodes, rx=rx, ry=ry,
+                      rw=rw)
+        gather_s, gather_d = split.sources.gather, split.destinations.gather
+        hx, hy, hw, hg = run_double_backward(op, gather_s(x), y, w, gather_d(g), gather_s(rx), ry, rw, split.graph,
+                                             needs)
+        return split.sources.reduce(hx), hy, hw, split.destinations.reduce(hg)
     struct, n, ns, e = _graph_struct(graph)
     _check_inputs(op, x, y, w, ns, e, g=g, num_nodes=n, rx=rx, ry=ry, rw=rw)
     x, y, w, g = _prepared(x), _prepared(y), _prepared(w), _prepared(g)

@@ -240,6 +240,14 @@ __device__ __forceinline__ void leave_tiles(unsigned* counters, int64_t total_wa
 }
 #endif
 
+// Edges per tile for the kernels that hand out tiles dynamically: `wanted` (64 unless overridden), but small enough
+// that every resident warp gets about eight tiles, so that a small launch (a piece of a shard, a small graph) does
+// not end with most warps idle while a few finish their last tile; never below 16 edges.
+inline int64_t tile_edges_for(int64_t num_edges, int64_t resident_warps, int64_t wanted) {
+  const int64_t spread = num_edges / std::max<int64_t>(8 * resident_warps, 1);
+  return std::max<int64_t>(1, std::min<int64_t>(wanted, std::max<int64_t>(16, spread)));
+}
+
 inline int64_t edges_per_warp(const Tuning& tuning, int64_t fallback) {
   return tuning.edges_per_warp > 0 ? tuning.edges_per_warp : fallback;
 }

@@ -16,7 +16,10 @@
 // a byte count) signal arrivals; every wait is bounded, and a wait that runs out sets the plan's status word and ends
 // the warp's loop.
 //
-// Work assignment.  Source nodes are cut into small tiles of consecutive nodes, handed out in ascending order: a
+// Work assignment.  Source nodes are cut into small tiles of consecutive nodes holding about the same number of edges
+// (tile t is the nodes whose edge lists begin in the t-th stretch of tile_edges positions of the source-sorted edge
+// order, found by a search in the row pointer: rows without edges, as the halo rows of a shard piece have many, cost
+// nothing and do not distort the tiles), handed out in ascending order: a
 // warp's first tile is its own number, further ones come from a counter (take_tile), so a warp that started late
 // takes fewer.  All resident warps work on neighbouring source nodes at any moment, and for a spatially ordered graph the
 // g[dst] rows they gather are the same few thousand rows, which stay in L2.  gx of a node is accumulated in registers
@@ -47,8 +50,8 @@ struct PlainParams {
   const T* sp_c;               // term coefficients of the plan (canon_toff order)
   const unsigned char* sp_j;   // y index of each term
   int* status;
-  int64_t num_src_nodes;
-  int64_t tile_nodes;
+  int64_t num_src_nodes, num_edges;
+  int64_t tile_edges;          // edges per tile (tiles are cut at node boundaries)
   unsigned* tile_counters;     // (next tile, warps finished)
   int slots, row_stages;
   int acc_x;                   // gx += instead of gx =
@@ -162,15 +165,17 @@ __device__ __forceinline__ void plain_loop(const PlainParams<T>& P, const PlainM
     alive = false;
   };
   const int64_t N = P.num_src_nodes;
-  const int64_t tile_nodes = P.tile_nodes;
-  const int64_t num_tiles = (N + tile_nodes - 1) / tile_nodes;
+  const int64_t tile_edges = P.tile_edges;
+  const int64_t num_tiles = (P.num_edges + tile_edges - 1) / tile_edges;
 
   int64_t tile = first_tile, tile_after = first_tile;
 #pragma unroll 1
   for (; tile < num_tiles && alive; tile = tile_after) {
     tile_after = take_tile(P.tile_counters, tile_step, lane);  // one ahead of need
-    const int64_t n_lo = tile * tile_nodes;
-    const int64_t n_hi = n_lo + tile_nodes < N ? n_lo + tile_nodes : N;
+    // tile t: the nodes whose edge lists begin in [t, t + 1) * tile_edges of the source-sorted edge order
+    const int64_t n_lo = tile == 0 ? 0 : warp_lower_bound(P.src_rowptr, N, tile * tile_edges, lane);
+    const int64_t n_hi = tile + 1 == num_tiles ? N : warp_lower_bound(P.src_rowptr, N, (tile + 1) * tile_edges, lane);
+    if (n_lo >= n_hi) continue;  // a node with more edges than a tile spans several tile numbers
     const int64_t p_begin = P.src_rowptr[n_lo], p_end = P.src_rowptr[n_hi];
     if (p_begin >= p_end) continue;
     const int total_units = static_cast<int>(p_end - p_begin) * nk;
@@ -241,7 +246,13 @@ __device__ __forceinline__ void plain_loop(const PlainParams<T>& P, const PlainM
 #pragma unroll 1
     for (int64_t n = n_lo; n < n_hi && alive; ++n) {
       const int64_t pe = P.src_rowptr[n + 1];
-      if (pos >= pe) continue;
+      if (pos >= pe) {
+        // A row without edges.  A shard piece has long runs of them (the sources its destinations do not read):
+        // jump to the row that holds the warp's next edge instead of walking the run one dependent load at a time.
+        if (pos >= p_end) break;  // nothing but such rows is left in the tile
+        n = warp_lower_bound(P.src_rowptr, N, pos + 1, lane) - 2;
+        continue;
+      }
       static_for<0, LX + 1>([&](auto l1c) {
         constexpr int l1 = decltype(l1c)::value;
         constexpr int d1 = 2 * l1 + 1;
@@ -449,12 +460,9 @@ int launch_fast_bwd_plain(const luna_uvu_plan* plan, const DeviceTables& dt, con
   if (warps == 0) return fail(LUNA_ERR_UNSUPPORTED, "backward needs more shared memory than the device has");
   P.slots = slots;
   P.row_stages = stages;
-  const int64_t rows = P.num_src_nodes;
-  const double degree = static_cast<double>(graph->num_edges) / static_cast<double>(std::max<int64_t>(rows, 1));
-  const int64_t tile_edges = edges_per_warp(plan->tuning, 64);
-  P.tile_nodes = std::max<int64_t>(1, static_cast<int64_t>(tile_edges / std::max(degree, 1e-3) + 0.5));
-  P.tile_nodes = std::min<int64_t>(P.tile_nodes, 1 << 20);
-  const int64_t num_tiles = ceil_div(rows, P.tile_nodes);
+  P.num_edges = graph->num_edges;
+  P.tile_edges = tile_edges_for(P.num_edges, static_cast<int64_t>(dt.sm_count) * warps, edges_per_warp(plan->tuning, 64));
+  const int64_t num_tiles = ceil_div(std::max<int64_t>(P.num_edges, 1), P.tile_edges);
   const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(dt.sm_count, ceil_div(num_tiles, warps)));
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));

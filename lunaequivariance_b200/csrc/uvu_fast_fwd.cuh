@@ -342,7 +342,9 @@ int launch_fast_fwd_one(const luna_uvu_plan* plan, const DeviceTables& dt, const
   // without this the driver may size the shared-memory carve-out for fewer CTAs than planned
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   const double degree = static_cast<double>(graph->num_edges) / static_cast<double>(std::max<int64_t>(graph->num_nodes, 1));
-  const int64_t tile_edges = plan->tuning.fwd_tile_edges > 0 ? plan->tuning.fwd_tile_edges : 64;
+  const int64_t tile_edges =
+      tile_edges_for(graph->num_edges, static_cast<int64_t>(dt.sm_count) * r.ctas * nwarps,
+                     plan->tuning.fwd_tile_edges > 0 ? plan->tuning.fwd_tile_edges : 64);
   P.tile_nodes = std::max<int64_t>(1, static_cast<int64_t>(tile_edges / std::max(degree, 1e-3) + 0.5));
   P.tile_nodes = std::min<int64_t>(P.tile_nodes, 1 << 20);
   const int64_t num_tiles = ceil_div(std::max<int64_t>(graph->num_nodes, 1), P.tile_nodes);

@@ -18,6 +18,9 @@ import torch
 from . import _native
 
 SOURCE_SEGMENT_EDGES = 32
+# A warp walks a node's edges one after the other, so a node with very many edges would hold one warp for the whole
+# launch.  Rows longer than this are cut into virtual rows of at most this many edges (LunaTPGraph.split_rows).
+ROW_SPLIT_EDGES = 1024
 
 
 @dataclass(frozen=True)
@@ -29,6 +32,58 @@ class SourceSegmentTables:
     end: torch.Tensor
     rowptr: torch.Tensor
     order: torch.Tensor
+
+
+class RowSplit:
+    """One side (destinations or sources) of a graph whose long rows were cut into virtual rows.
+
+    ``rows[v]`` is the real node of virtual row ``v`` (pieces of a node are consecutive virtual rows); ``gather``
+    expands node rows to virtual rows, ``reduce`` sums virtual rows back to node rows, adding the pieces of a node in
+    ascending order so that results are reproducible.
+    """
+
+    def __init__(self, rowptr: torch.Tensor, limit: int):
+        degree = rowptr.to(torch.int64).diff()
+        pieces = torch.clamp((degree + limit - 1) // limit, min=1)
+        self.first = torch.cumsum(pieces, 0) - pieces             # first virtual row of each node
+        self.virtual_rows = int(pieces.sum())
+        self.rows = torch.repeat_interleave(torch.arange(degree.numel(), device=rowptr.device), pieces)
+        self.limit = limit
+        # nodes that have a (j + 1)-th piece, for j = 1, 2, ...: the targets of the j-th round of additions
+        self.rounds = []
+        for j in range(1, int(pieces.max()) if degree.numel() else 1):
+            nodes = torch.nonzero(pieces > j).squeeze(1)
+            self.rounds.append((nodes, self.first[nodes] + j))
+
+    def gather(self, tensor: torch.Tensor | None) -> torch.Tensor | None:
+        return None if tensor is None else tensor.index_select(0, self.rows)
+
+    def reduce(self, virtual: torch.Tensor | None) -> torch.Tensor | None:
+        if virtual is None:
+            return None
+        out = virtual.index_select(0, self.first)
+        for nodes, rows in self.rounds:  # distinct targets within a round: plain indexed add, fixed order
+            out[nodes] += virtual[rows]
+        return out
+
+
+class SplitGraph:
+    """A graph with the same edges in the same order whose long rows are virtual rows (see ``ROW_SPLIT_EDGES``)."""
+
+    def __init__(self, graph: "LunaTPGraph", limit: int):
+        self.destinations = RowSplit(graph.dst_rowptr, limit)
+        self.sources = RowSplit(graph.src_rowptr, limit)
+        edges = graph.num_edges
+        position = torch.arange(edges, device=graph.src.device, dtype=torch.int64)
+        dst = graph.dst.to(torch.int64)
+        dst_virtual = self.destinations.first[dst] + (position - graph.dst_rowptr.to(torch.int64)[dst]) // limit
+        by_src = graph.edge_ids_by_src.to(torch.int64)
+        src_sorted = graph.src.to(torch.int64)[by_src]
+        rank = position - graph.src_rowptr.to(torch.int64)[src_sorted]  # of an edge among its source's edges
+        src_virtual = torch.empty_like(position)
+        src_virtual[by_src] = self.sources.first[src_sorted] + rank // limit
+        self.graph = make_graph(src_virtual, dst_virtual, self.destinations.virtual_rows,
+                                num_src_nodes=self.sources.virtual_rows, split=False)
 
 
 @dataclass(frozen=True)
@@ -49,6 +104,7 @@ class LunaTPGraph:
     # Rows of x / gx.  Equals num_nodes except on a destination-range shard of a partitioned graph, where the
     # sources keep their global numbering (no counterpart in the reference, which is single-GPU).
     num_src_nodes: int | None = None
+    can_split: bool = True  # False for the virtual-row graphs themselves
     _tables: dict = field(default_factory=dict, init=False, repr=False, compare=False)
 
     @property
@@ -88,6 +144,18 @@ class LunaTPGraph:
             piece = make_graph(self.src[e0:e1], self.dst[e0:e1] - begin, end - begin, num_src_nodes=self.source_rows)
             cached = self._tables[key] = (piece, e0, e1)
         return cached
+
+    def split_rows(self) -> "SplitGraph | None":
+        """The virtual-row form of this graph if a node has more than ``ROW_SPLIT_EDGES`` edges on either side, else
+        ``None``.  Decided once per graph (one read of the largest degree) and cached."""
+        if "split" not in self._tables:
+            split = None
+            if self.can_split and self.num_edges:
+                longest = int(torch.maximum(self.dst_rowptr.diff().max(), self.src_rowptr.diff().max()))
+                if longest > ROW_SPLIT_EDGES:
+                    split = SplitGraph(self, ROW_SPLIT_EDGES)
+            self._tables["split"] = split
+        return self._tables["split"]
 
     def table_list(self) -> list:
         """The 13 tensors the reference passes to its custom ops (``src/lunatp/uvu_conv/interface.py:186-192``)."""
@@ -143,13 +211,14 @@ def _bounds_cuda(src, dst):
 
 
 def make_graph(src: torch.Tensor, dst: torch.Tensor, num_nodes: int | None = None, *,
-               num_src_nodes: int | None = None) -> LunaTPGraph:
+               num_src_nodes: int | None = None, split: bool = True) -> LunaTPGraph:
     """Build the topology tables from a destination-sorted edge list.
 
     ``src`` and ``dst`` are ``[edges]`` or ``[edges, 1]`` int32/int64 tensors on one device, ``dst`` ascending and
     all edge data in the same order.  Build once per topology and reuse across layers.  ``num_src_nodes`` (keyword
     only, default ``num_nodes``) gives the row count of ``x`` when sources are numbered in a larger range than the
-    destinations, as on one shard of a partitioned graph.
+    destinations, as on one shard of a partitioned graph.  ``split=False`` marks a graph whose rows must stay as
+    they are (``split_rows`` then returns ``None``).
     """
     if src.ndim == 2 and src.shape[1] == 1:
         src = src.squeeze(-1)
@@ -205,6 +274,7 @@ def make_graph(src: torch.Tensor, dst: torch.Tensor, num_nodes: int | None = Non
         node_tiers=_node_tiers(dst_rowptr, node_order, num_nodes, num_edges, device),
         source_segments=make_source_segments(src_rowptr),
         num_src_nodes=None if num_src_nodes is None else source_rows,
+        can_split=split,
     )
     return graph
 
@@ -254,4 +324,4 @@ def _build_cuda(src, dst, num_nodes, source_rows):
     return tuple(out)
 
 
-__all__ = ["LunaTPGraph", "SourceSegmentTables", "make_graph", "make_source_segments"]
+__all__ = ["LunaTPGraph", "SourceSegmentTables", "SplitGraph", "RowSplit", "make_graph", "make_source_segments"]
