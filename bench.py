@@ -63,8 +63,11 @@ def parse_args():
     p.add_argument("--skip-others", action="store_true")
     p.add_argument("--cpu-seconds", type=float, default=15.0)
     p.add_argument("--generic", action="store_true", help="force the table-driven kernels")
-    p.add_argument("--no-overlap", action="store_true",
-                   help="N > 1: exchange, forward, backward, return one after the other on one stream")
+    p.add_argument("--overlap", action="store_true",
+                   help="N > 1: hide the halo exchanges behind the interior piece of the shard (sharded."
+                        "overlapped_step) instead of exchange, forward, backward, return one after the other; "
+                        "measured slower at N = 2 and N = 8 on cfg2 (three launches per pass cost more than the "
+                        "exchanges), so it is not the default")
     p.add_argument("--e2e-chunks", type=int, default=32, help="pieces of the host-streamed step")
     return p.parse_args()
 
@@ -326,7 +329,7 @@ def time_steps(step, steps, warmup, marks, world, sampler=None):
 class ConvWorkload:
     """One workload's tensors on this rank, the step that is timed, and its accounting."""
 
-    def __init__(self, name, atoms, world, rank, device, generic=False, overlap=True):
+    def __init__(self, name, atoms, world, rank, device, generic=False, overlap=False):
         import lunaequivariance_b200 as luna
         from lunaequivariance_b200 import sharded
 
@@ -578,7 +581,7 @@ def sharded_parity(world, rank, device):
 # ------------------------------------------------------------------------------------------------- native arm
 
 
-def measure_others(world, rank, device, main_name, peaks, overlap=True):
+def measure_others(world, rank, device, main_name, peaks, overlap=False):
     """Brief measurements of the workloads that are not the headline, so that one run records them all."""
     others = {}
     if world == 1:
@@ -658,7 +661,7 @@ def main():
         return
 
     work = ConvWorkload(args.workload, args.atoms_per_gpu, world, rank, device, args.generic,
-                        overlap=not args.no_overlap)
+                        overlap=args.overlap)
     result = work.measure(args.steps, args.warmup, sampler)
     clocks = sampler.stop() if sampler else None
     op_status = None
@@ -677,7 +680,7 @@ def main():
     if not args.skip_others:
         if world == 1:
             peaks = fma_peaks(device)
-        others = measure_others(world, rank, device, name, peaks, overlap=not args.no_overlap)
+        others = measure_others(world, rank, device, name, peaks, overlap=args.overlap)
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         cpu = cpu_sample_rate(name, args.cpu_seconds, args.atoms_per_gpu)
@@ -686,7 +689,7 @@ def main():
         # kernels of this library per step: forward + backward (+ the harmonics and second-order launches of cfg3)
         # (a partitioned step with overlap runs forward and backward as up to three pieces each)
         launches_per_step = 9 if name == "cfg3" else (2 if staged else 4)
-        if world > 1 and not args.no_overlap and name != "cfg3":
+        if world > 1 and args.overlap and name != "cfg3":
             launches_per_step *= pieces
         line = {
             "metric": "uvu_conv_fwd_bwd_edges_per_s", "value": result["value"], "unit": "edges/s",
