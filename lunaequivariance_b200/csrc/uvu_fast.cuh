@@ -202,6 +202,31 @@ __device__ __forceinline__ int64_t warp_lower_bound(const int* __restrict__ rowp
   return lo + __popc(__ballot_sync(0xffffffffu, below));
 }
 
+// The same answer as warp_lower_bound(rowptr, count, bound, lane) when it is known to be at or after `from` and is
+// expected within 32 entries of it (one coalesced load); falls back to the search otherwise.
+__device__ __forceinline__ int64_t warp_lower_bound_near(const int* __restrict__ rowptr, int64_t count, int64_t bound,
+                                                         int64_t from, int lane) {
+  const int64_t idx = from + lane;
+  const bool below = idx < count && rowptr[idx] < bound;
+  const unsigned mask = __ballot_sync(0xffffffffu, below);
+  if (mask != 0xffffffffu) return from + __popc(mask);  // rowptr is ascending: the lanes below form a prefix
+  return warp_lower_bound(rowptr, count, bound, lane);
+}
+
+// The same answer again, from a guess of where it lies: one coalesced load of the 32 entries around the guess settles
+// it when the answer is among them (the first of them below the bound, not all of them), the search otherwise.
+__device__ __forceinline__ int64_t warp_lower_bound_guess(const int* __restrict__ rowptr, int64_t count, int64_t bound,
+                                                          int64_t guess, int lane) {
+  int64_t base = guess - 16;
+  if (base > count - 16) base = count - 16;
+  if (base < 0) base = 0;
+  const int64_t idx = base + lane;
+  const bool below = idx < count && rowptr[idx] < bound;
+  const unsigned mask = __ballot_sync(0xffffffffu, below);
+  if ((base == 0 || (mask & 1u)) && mask != 0xffffffffu) return base + __popc(mask);
+  return warp_lower_bound(rowptr, count, bound, lane);
+}
+
 // How a staged kernel is made resident: ring depth per warp, warps per CTA, CTAs per SM, dynamic shared memory.
 struct Residency {
   int depth = 0;  // stages / slots per warp, 0 if nothing fits

@@ -52,9 +52,12 @@ struct PlainParams {
   int* status;
   int64_t num_src_nodes, num_edges;
   int64_t tile_edges;          // edges per tile (tiles are cut at node boundaries)
+  int64_t tile_nodes;          // > 0: tiles are this many nodes instead (graphs whose rows all have edges)
+  int64_t num_tiles;
   unsigned* tile_counters;     // (next tile, warps finished)
   int slots, row_stages;
   int acc_x;                   // gx += instead of gx =
+  float rows_per_edge;         // source rows / edges: the average the tile search guesses with
   int two;                     // always 2: source of the run-time 1.0 that settles freshly assembled pairs
 };
 
@@ -166,17 +169,29 @@ __device__ __forceinline__ void plain_loop(const PlainParams<T>& P, const PlainM
   };
   const int64_t N = P.num_src_nodes;
   const int64_t tile_edges = P.tile_edges;
-  const int64_t num_tiles = (P.num_edges + tile_edges - 1) / tile_edges;
+  const int64_t num_tiles = P.num_tiles;
 
   int64_t tile = first_tile, tile_after = first_tile;
+  int64_t seen_node = 0, seen_pos = 0;  // a node boundary this warp has seen, and where its edges begin
 #pragma unroll 1
   for (; tile < num_tiles && alive; tile = tile_after) {
     tile_after = take_tile(P.tile_counters, tile_step, lane);  // one ahead of need
-    // tile t: the nodes whose edge lists begin in [t, t + 1) * tile_edges of the source-sorted edge order
-    const int64_t n_lo = tile == 0 ? 0 : warp_lower_bound(P.src_rowptr, N, tile * tile_edges, lane);
-    const int64_t n_hi = tile + 1 == num_tiles ? N : warp_lower_bound(P.src_rowptr, N, (tile + 1) * tile_edges, lane);
+    int64_t n_lo, n_hi;
+    if (P.tile_nodes > 0) {
+      n_lo = tile * P.tile_nodes;
+      n_hi = n_lo + P.tile_nodes < N ? n_lo + P.tile_nodes : N;
+    } else {
+      // tile t: the nodes whose edge lists begin in [t, t + 1) * tile_edges of the source-sorted edge order
+      // (guessed from where the warp's previous tile ended, assuming rows of average length in between)
+      const int64_t guess =
+          seen_node + static_cast<int64_t>(static_cast<float>(tile * tile_edges - seen_pos) * P.rows_per_edge);
+      n_lo = tile == 0 ? 0 : warp_lower_bound_guess(P.src_rowptr, N, tile * tile_edges, guess, lane);
+      n_hi = tile + 1 == num_tiles ? N : warp_lower_bound_near(P.src_rowptr, N, (tile + 1) * tile_edges, n_lo, lane);
+    }
     if (n_lo >= n_hi) continue;  // a node with more edges than a tile spans several tile numbers
     const int64_t p_begin = P.src_rowptr[n_lo], p_end = P.src_rowptr[n_hi];
+    seen_node = n_hi;
+    seen_pos = p_end;
     if (p_begin >= p_end) continue;
     const int total_units = static_cast<int>(p_end - p_begin) * nk;
 
@@ -461,8 +476,18 @@ int launch_fast_bwd_plain(const luna_uvu_plan* plan, const DeviceTables& dt, con
   P.slots = slots;
   P.row_stages = stages;
   P.num_edges = graph->num_edges;
+  P.rows_per_edge = static_cast<float>(static_cast<double>(P.num_src_nodes) / static_cast<double>(std::max<int64_t>(P.num_edges, 1)));
   P.tile_edges = tile_edges_for(P.num_edges, static_cast<int64_t>(dt.sm_count) * warps, edges_per_warp(plan->tuning, 64));
-  const int64_t num_tiles = ceil_div(std::max<int64_t>(P.num_edges, 1), P.tile_edges);
+  // A whole graph (as many source rows as destination rows) of some density has hardly any rows without edges, and
+  // a fixed number of nodes per tile then gives even tiles without any search: measured 5 % faster than edge-count
+  // tiles on the 50,000-atom radius graph.  Shards and pieces of graphs have long runs of rows without edges and
+  // get edge-count tiles.
+  const bool whole = graph->num_src_nodes <= 0 || graph->num_src_nodes == graph->num_nodes;
+  const double degree = static_cast<double>(P.num_edges) / static_cast<double>(std::max<int64_t>(P.num_src_nodes, 1));
+  P.tile_nodes = (whole && degree >= 8.0) ? std::max<int64_t>(1, static_cast<int64_t>(P.tile_edges / degree + 0.5)) : 0;
+  const int64_t num_tiles = P.tile_nodes > 0 ? ceil_div(std::max<int64_t>(P.num_src_nodes, 1), P.tile_nodes)
+                                             : ceil_div(std::max<int64_t>(P.num_edges, 1), P.tile_edges);
+  P.num_tiles = num_tiles;
   const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(dt.sm_count, ceil_div(num_tiles, warps)));
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_bytes)));
   LUNA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
