@@ -41,8 +41,8 @@ from bench_workloads import CUTOFF, DENSITY, WORKLOADS, build_graph_edges, build
 # atoms); a run on another atom count scales them by its edges, which is what the traffic grows with.  A run whose plan
 # picks another variant reports null.
 NCU_TRAFFIC_BYTES_PER_EDGE = {
-    ("cfg2", "forward", "staged"): 10.20e3,
-    ("cfg2", "backward", "row"): 19.50e3,
+    ("cfg2", "forward", "staged"): 9.48e3,
+    ("cfg2", "backward", "row"): 18.31e3,
 }
 SH6_ITEMS = 4_000_000
 # algorithmic FLOPs per edge of the forward pass (sum over paths of channels * (2 * terms + d2))
