@@ -531,8 +531,27 @@ sh_canon_kernel(const ShParams P, const T* __restrict__ v, const T* __restrict__
     }
     if constexpr (MODE != 0) {
       const T* gsrc = g + base * C;
+      if (rows == 32) {
+        // a full tile: the loads go out in batches of eight per lane before anything is stored, so that a warp has
+        // 1 KB (FP32) in flight instead of one row of loads waiting on the next
+        constexpr int kBatch = 8;
+#pragma unroll
+        for (int j0 = 0; j0 < C; j0 += kBatch) {
+          T batch[kBatch];
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j)
+            if (j0 + j < C) batch[j] = gsrc[(j0 + j) * 32 + lane];
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j)
+            if (j0 + j < C) {
+              const int idx = (j0 + j) * 32 + lane;
+              tile[(idx / C) * CP + (idx % C)] = batch[j];
+            }
+        }
+      } else {
 #pragma unroll 4
-      for (int idx = lane; idx < rows * C; idx += 32) tile[(idx / C) * CP + (idx % C)] = gsrc[idx];
+        for (int idx = lane; idx < rows * C; idx += 32) tile[(idx / C) * CP + (idx % C)] = gsrc[idx];
+      }
       __syncwarp();
     }
     if constexpr (MODE == 0) {
