@@ -484,6 +484,42 @@ def measure_sh6(steps, warmup, device):
             "algorithmic_bytes": {"forward": fwd_bytes, "forward_backward": both_bytes}}
 
 
+def measure_cfg1_graph(device, steps=200):
+    """The reference's CPU-runnable configuration (1,000 atoms, 16,000 edges, FP64): a step is launch-bound, so it is
+    timed both as eager calls and as one captured CUDA graph replayed."""
+    work = ConvWorkload("cfg1", None, 1, 0, device)
+
+    def step():
+        work.step(None)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    captured = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(captured):
+        step()
+
+    def timed(fn):
+        for _ in range(10):
+            fn()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps
+
+    eager_ms, graph_ms = timed(step), timed(captured.replay)
+    return {"edges": work.edges, "dtype": "f64", "eager_ms": eager_ms, "cuda_graph_ms": graph_ms,
+            "edges_per_s_eager": work.edges / (eager_ms * 1e-3), "edges_per_s_cuda_graph": work.edges / (graph_ms * 1e-3),
+            "step": "forward + backward (gx, gy, gw), " + str(steps) + " back-to-back steps"}
+
+
 def fma_peaks(device):
     """Register-resident FMA chains: the packed-FP32 and the FP64 arithmetic peaks of this GPU, measured."""
     import ctypes
@@ -610,6 +646,10 @@ def measure_others(world, rank, device, main_name, peaks, overlap=False):
             others["sh6"] = measure_sh6(5, 3, device)
         except Exception as error:
             others["sh6"] = {"error": f"{type(error).__name__}: {error}"[:300]}
+        try:
+            others["cfg1"] = measure_cfg1_graph(device)
+        except Exception as error:
+            others["cfg1"] = {"error": f"{type(error).__name__}: {error}"[:300]}
     elif main_name != "cfg5":
         try:  # the partitioned configuration itself: 250,000 atoms per GPU
             work = ConvWorkload("cfg5", None, world, rank, device, overlap=overlap)
