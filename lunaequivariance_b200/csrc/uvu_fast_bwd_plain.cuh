@@ -31,6 +31,9 @@
 namespace luna {
 namespace fastk {
 
+// A stage is refilled after the first unit of the next edge: by then the bulk store of the row that was in it has
+// read the stage.  Refilling one unit later measured 1 % slower (the row then has less time to arrive).
+constexpr int kPlainRefillUnit = 0;
 constexpr int kPlainMaxStages = 4;  // weight-row stages per warp (at most; the launcher picks 2..4)
 constexpr int kPlainMaxSlots = 4;   // slots of a warp's g ring (at most)
 constexpr int kPlainBarriers = kPlainMaxStages + kPlainMaxSlots;  // row landed, per stage; g block landed, per slot
@@ -299,7 +302,7 @@ __device__ __forceinline__ void plain_loop(const PlainParams<T>& P, const PlainM
         static_for<0, LO + 1>([&](auto l3c) {
           constexpr int kind = decltype(l3c)::value;
           if (alive) run_unit(l3c, wrow);
-          if constexpr (kind == 0) {
+          if constexpr (kind == kPlainRefillUnit) {
             if (refill_stage >= 0 && alive) {  // the row this warp sent back has been read out of its stage by now
               if (lane == 0) {
                 bulk_wait_group_read_all();
