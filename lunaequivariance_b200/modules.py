@@ -15,7 +15,7 @@ from .functional import require_uvu, resolve_source, tensor_product, tensor_prod
 from .graph import make_graph
 from .paths import TensorProductConfig
 from .tensor_product import LunaTPUVU
-from .spherical_harmonics import UNSET, SphericalHarmonicsConfig, parse_irreps, spherical_harmonics
+from .spherical_harmonics import UNSET, SphericalHarmonicsConfig, spherical_harmonics
 
 
 class TensorProductConv(torch.nn.Module):

@@ -1,6 +1,5 @@
 """Parity of the CUDA convolution (through the C-ABI) with the CPU oracle: forward, first and second derivatives."""
 
-import numpy as np
 import pytest
 import torch
 

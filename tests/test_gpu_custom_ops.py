@@ -10,7 +10,6 @@ import pytest
 import torch
 
 import lunaequivariance_b200 as luna
-from lunaequivariance_b200 import conv as conv_mod
 from oracle import uvu_conv as oracle_conv
 from tests.helpers import assert_close, config, random_graph, random_problem
 
