@@ -108,3 +108,37 @@ def test_radius_graph_matches_reference_kernels(name, dtype, atoms):
     p = dict(x=rand(atoms, op.in1_dim), y=y, w=rand(edges, op.weight_numel), g=rand(atoms, op.out_dim),
              rx=rand(atoms, op.in1_dim), ry=rand(edges, op.in2_dim), rw=rand(edges, op.weight_numel))
     _compare(name, dtype, module, reference, graph, p)
+
+
+def test_config2_at_full_size_matches_reference_kernels_everywhere():
+    """BASELINE configuration 2 at its size (50,000 atoms, 2.6 M edges, FP32): every element of out, gx, gy and gw
+    against the reference's own kernels on the same GPU (its 64-bit index variant at this size)."""
+    name, dtype, atoms = "cfg2", torch.float32, 50_000
+    if not ref_kernels.available(_key(name, dtype)):
+        pytest.skip("oracle/_ref holds no build of the reference's kernels for this configuration")
+    in1, in2, out, instructions, _ = config(name)
+    module = luna.TensorProductConv(in1, in2, out, instructions, internal_weights=False, shared_weights=False,
+                                    dtype=dtype)
+    reference = ref_kernels.ReferenceKernels(_key(name, dtype))
+    pos, box, cells = workloads.periodic_positions(atoms, workloads.DENSITY, 0, DEVICE, workloads.CUTOFF)
+    src, dst, vec = workloads.radius_graph_periodic(pos, box, workloads.CUTOFF, cells)
+    graph = module.create_graph(src, dst, atoms)
+    op = module.op
+    y = luna.spherical_harmonics([0, 1, 2, 3], vec.to(dtype), True, "component").contiguous()
+    generator = torch.Generator(device=DEVICE).manual_seed(31)
+    rand = lambda *shape: torch.randn(*shape, device=DEVICE, dtype=dtype, generator=generator)
+    x, w, g = rand(atoms, op.in1_dim), rand(graph.num_edges, op.weight_numel), rand(atoms, op.out_dim)
+
+    def worst(mine, theirs):  # on the device: the tensors are GBs
+        scale = theirs.abs().max().clamp_min(1e-30)
+        return float((mine - theirs).abs().max() / scale)
+
+    errors = {"out": worst(conv_mod.run_forward(op, x, y, w, graph), reference.forward(x, y, w, graph))}
+    mine, theirs = conv_mod.run_backward(op, x, y, w, g, graph), reference.backward(x, y, w, g, graph)
+    for what, a, b in zip(("gx", "gy", "gw"), mine, theirs):
+        errors[what] = worst(a, b)
+    del mine, theirs
+    torch.cuda.empty_cache()
+    op.check_status()
+    assert graph.num_edges > 2_000_000
+    assert all(e <= 1e-5 for e in errors.values()), errors
