@@ -110,10 +110,12 @@ def test_radius_graph_matches_reference_kernels(name, dtype, atoms):
     _compare(name, dtype, module, reference, graph, p)
 
 
-def test_config2_at_full_size_matches_reference_kernels_everywhere():
-    """BASELINE configuration 2 at its size (50,000 atoms, 2.6 M edges, FP32): every element of out, gx, gy and gw
-    against the reference's own kernels on the same GPU (its 64-bit index variant at this size)."""
-    name, dtype, atoms = "cfg2", torch.float32, 50_000
+@pytest.mark.parametrize("dtype,atoms,tol", [(torch.float32, 50_000, 1e-5), (torch.float64, 20_000, 1e-12)])
+def test_config2_at_full_size_matches_reference_kernels_everywhere(dtype, atoms, tol):
+    """BASELINE configurations 2 (FP32, 50,000 atoms, 2.6 M edges) and 3's convolution (FP64, 20,000 atoms, 1.0 M
+    edges) at their sizes: every element of out, gx, gy and gw against the reference's own kernels on the same GPU
+    (its 64-bit index variant at these sizes)."""
+    name = "cfg2"
     if not ref_kernels.available(_key(name, dtype)):
         pytest.skip("oracle/_ref holds no build of the reference's kernels for this configuration")
     in1, in2, out, instructions, _ = config(name)
@@ -140,5 +142,5 @@ def test_config2_at_full_size_matches_reference_kernels_everywhere():
     del mine, theirs
     torch.cuda.empty_cache()
     op.check_status()
-    assert graph.num_edges > 2_000_000
-    assert all(e <= 1e-5 for e in errors.values()), errors
+    assert graph.num_edges > 1_000_000
+    assert all(e <= tol for e in errors.values()), errors
