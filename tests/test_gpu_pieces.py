@@ -123,3 +123,33 @@ def test_overlapped_step_on_one_rank_of_a_partition(rank):
     assert events[0].elapsed_time(events[4]) > 0
     assert torch.equal(out, ref_out) and torch.equal(gy, ref_gy) and torch.equal(gw, ref_gw)
     assert_close(gx_full, ref_gx.cpu(), dtype, f"rank {rank} gx of the compact buffer")
+
+
+def test_host_streamed_step_on_tiny_and_empty_graphs():
+    in1, in2, out, instructions, _ = config("fixture")
+    dtype = torch.float32
+    module = luna.TensorProductConv(in1, in2, out, instructions, internal_weights=False, shared_weights=False,
+                                    dtype=dtype)
+    op = module.op
+    nodes = 7
+    dst = torch.tensor([0, 0, 1, 1, 1, 4, 4, 4, 4, 6], device=DEVICE)  # destinations 2, 3, 5 have no edge
+    src = torch.tensor([1, 6, 0, 2, 3, 4, 5, 0, 1, 2], device=DEVICE)
+    graph = luna.make_graph(src, dst, nodes)
+    generator = torch.Generator(device=DEVICE).manual_seed(2)
+    rand = lambda *shape: torch.randn(*shape, generator=generator, dtype=dtype, device=DEVICE)
+    t = dict(x=rand(nodes, op.in1_dim), y=rand(10, op.in2_dim), w=rand(10, op.weight_numel), g=rand(nodes, op.out_dim))
+    ref = whole(op, graph, t)
+    streamed = HostStreamedConv(op, graph, chunks=16)  # more chunks than nodes
+    assert 1 <= len(streamed.pieces) <= nodes
+    host = {k: v.cpu() for k, v in t.items()}  # pageable memory works too
+    out_rows, gx, gy, gw = streamed.step(host["x"], host["y"], host["w"], host["g"])
+    assert torch.equal(out_rows, ref["out"].cpu()) and torch.equal(gy, ref["gy"].cpu())
+    assert torch.equal(gw, ref["gw"].cpu())
+    assert_close(gx, ref["gx"].cpu(), dtype, "tiny graph gx")
+    assert not out_rows[[2, 3, 5]].any()
+
+    empty = luna.make_graph(src[:0], dst[:0], 4)
+    streamed = HostStreamedConv(op, empty, chunks=3)
+    out_rows, gx, gy, gw = streamed.step(host["x"][:4], host["y"][:0], host["w"][:0], host["g"][:4])
+    assert out_rows.shape == (4, op.out_dim) and not out_rows.any() and not gx.any()
+    assert gy.shape == (0, op.in2_dim) and gw.shape == (0, op.weight_numel)
