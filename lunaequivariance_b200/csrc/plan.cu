@@ -56,6 +56,7 @@ bool fill_layout(luna_uvu_plan* plan, FastMeta& f, int cpl) {
   const int chw = 32 * cpl;
   if (ch % chw != 0) return false;
   f.chunks = ch / chw;
+  if (f.chunks > kTileCounterWords / 2) return false;  // one pair of tile counters per channel chunk
   f.ch = ch;
   f.X = plan->X;
   f.Y = plan->Y;

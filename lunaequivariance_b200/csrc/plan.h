@@ -124,7 +124,7 @@ struct Tuning {
 Tuning tuning_from_environment();
 
 constexpr int kTileCounterSets = 32;    // launches of one plan that may be in flight on a device at a time
-constexpr int kTileCounterWords = 16;   // per set: (next tile, warps finished) for up to 8 channel chunks
+constexpr int kTileCounterWords = 64;   // per set: (next tile, warps finished) for up to 32 channel chunks
 
 struct DeviceTables {
   void* buffer = nullptr;  // one allocation holding every table
