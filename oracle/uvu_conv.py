@@ -19,8 +19,10 @@ Parity pin: the path tables produced here are compared with tables dumped from t
 ``TensorProductPaths`` / ``build_uvu_conv_metadata`` / ``wigner_3j`` (``tests/golden/reference_tables.json`` and
 ``reference_wigner.npz``, written by ``tests/golden/make_golden.py``), the convolution values with vectors computed
 from the reference's metadata (``tests/golden/conv_vectors.npz``) and with the closed form of
-``examples/basic_uvu_conv.py:35-38``.  No stored end-to-end vectors of the reference's CUDA kernels exist (they
-cannot run without a GPU), so beyond those pins parity is "unpinned".
+``examples/basic_uvu_conv.py:35-38``.  The reference's CUDA kernels cannot run without a GPU, so no stored vectors
+of theirs exist; instead ``oracle/build_ref.py`` compiles the kernels the reference generates and
+``tests/test_gpu_reference_kernels.py`` runs them beside the library on the same GPU and inputs (small graphs to
+second order, and two configurations at full size element by element): that is the pin of the convolution values.
 """
 
 from __future__ import annotations
