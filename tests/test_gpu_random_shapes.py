@@ -1,0 +1,65 @@
+"""Seeded random graph shapes against the CPU oracle: sizes and degree distributions the fixed cases do not have.
+
+Single nodes, graphs with fewer edges than resident warps, many nodes without edges on either side, skewed degrees,
+one-edge graphs: the tile hand-out, the jump over empty rows and the small-launch tile sizes all have their corner
+cases here.  Every case runs forward, the three first derivatives and (for the smaller ones) the second derivatives.
+"""
+
+import pytest
+import torch
+
+import lunaequivariance_b200 as luna
+from oracle import uvu_conv as oracle_conv
+from tests.helpers import assert_close, config, random_problem
+
+pytestmark = pytest.mark.gpu
+DEVICE = "cuda"
+NAMES = ("fixture", "cfg5", "cfg2", "cfg4", "partial", "wide", "cfg1")
+
+
+def skewed_graph(nodes, edges, generator, skew):
+    """Destination-sorted edges; with ``skew`` > 0 both end points prefer low node numbers (power law), so that a
+    few nodes hold most edges and many hold none."""
+    def draw():
+        u = torch.rand(edges, generator=generator, dtype=torch.float64)
+        return torch.clamp((u ** (1.0 + skew) * nodes).long(), max=nodes - 1)
+    src, dst = draw(), torch.sort(draw())[0]
+    return src, dst
+
+
+@pytest.mark.parametrize("seed", range(28))
+def test_random_shape(seed):
+    generator = torch.Generator().manual_seed(1000 + seed)
+    pick = lambda n: int(torch.randint(n, (1,), generator=generator))
+    name = NAMES[pick(len(NAMES))]
+    dtype = (torch.float32, torch.float64)[pick(2)]
+    nodes = (1, 2, 7, 64, 257, 900)[pick(6)]
+    edges = (1, 3, 40, 700, 5000)[pick(5)]
+    if name in ("cfg2", "cfg4", "wide"):
+        edges = min(edges, 700)  # wide rows: keep the oracle quick
+    skew = (0.0, 0.0, 1.5, 4.0)[pick(4)]
+    in1, in2, out, instructions, options = config(name)
+    module = luna.TensorProductConv(in1, in2, out, instructions, internal_weights=False, shared_weights=False,
+                                    dtype=dtype, **options)
+    meta = oracle_conv.build_specs(in1, in2, out, instructions, **options)
+    src, dst = skewed_graph(nodes, edges, generator, skew)
+    dims = (meta["in1_dim"], meta["in2_dim"], meta["out_dim"], meta["weight_numel"])
+    p = random_problem(dims, nodes, src, dtype, generator)
+    second = edges <= 700
+    ref = oracle_conv.conv_derivatives(
+        meta, *(p[k].double() for k in ("x", "y", "w")), src, dst, nodes, p["g"].double(),
+        *((p[k].double() for k in ("rx", "ry", "rw")) if second else (None, None, None)))
+    graph = module.create_graph(src.to(DEVICE), dst.to(DEVICE), nodes)
+    x, y, w, g = (p[k].to(DEVICE).requires_grad_(True) for k in ("x", "y", "w", "g"))
+    what = f"seed {seed}: {name} {dtype} nodes {nodes} edges {edges} skew {skew}"
+    result = module(x, y, w, graph=graph)
+    assert_close(result, ref["out"], dtype, what + " out")
+    gx, gy, gw = torch.autograd.grad(result, (x, y, w), g, create_graph=second)
+    for key, value in (("gx", gx), ("gy", gy), ("gw", gw)):
+        assert_close(value, ref[key], dtype, f"{what} {key}")
+    if second:
+        seeds = tuple(p[k].to(DEVICE) for k in ("rx", "ry", "rw"))
+        hx, hy, hw, hg = torch.autograd.grad((gx, gy, gw), (x, y, w, g), seeds)
+        for key, value in (("hx", hx), ("hy", hy), ("hw", hw), ("hg", hg)):
+            assert_close(value, ref[key], dtype, f"{what} {key}")
+    module.op.check_status()
