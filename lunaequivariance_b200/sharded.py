@@ -137,10 +137,15 @@ def return_halo(full: torch.Tensor, shard: GraphShard) -> torch.Tensor:
     incoming = full.new_empty((sum(shard.send_counts), *full.shape[1:]))
     dist.all_to_all_single(incoming, full[local:].contiguous(), output_split_sizes=list(shard.send_counts),
                            input_split_sizes=list(shard.recv_counts), group=shard.group)
-    own = full[:local].clone()
+    return _add_returned_rows(full[:local].clone(), incoming, shard)
+
+
+def _add_returned_rows(own: torch.Tensor, incoming: torch.Tensor, shard: GraphShard) -> torch.Tensor:
+    """Adds the gradient rows that came back from the other ranks to the owned rows, one requesting rank after the
+    other: the rows one rank asked for are distinct, so each of these adds has a fixed result."""
     offset = 0
     for count in shard.send_counts:
-        if count:  # the rows one rank asked for are distinct, so each of these adds has a fixed result
+        if count:
             own.index_add_(0, shard.send_rows[offset:offset + count], incoming[offset:offset + count])
             offset += count
     return own
@@ -291,11 +296,7 @@ def overlapped_step(op, x_local: torch.Tensor, edge_attr: torch.Tensor, weight: 
         return out, (gx_full if halo_rows is not None else gx_full[:local]), gy, gw
     main.wait_event(returned)
     incoming.record_stream(main)
-    own, offset = gx_full[:local], 0
-    for count in shard.send_counts:
-        if count:
-            own.index_add_(0, shard.send_rows[offset:offset + count], incoming[offset:offset + count])
-            offset += count
+    own = _add_returned_rows(gx_full[:local], incoming, shard)
     mark(4)
     return out, own, gy, gw
 
