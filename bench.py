@@ -52,8 +52,8 @@ FORWARD_FLOPS_PER_EDGE = {"cfg1": 288, "cfg2": 64128, "cfg3": 64128, "cfg4": 515
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=30)
-    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="native", choices=["native", "reference"])
     p.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["sh6"])
     p.add_argument("--atoms-per-gpu", type=int, default=None)
