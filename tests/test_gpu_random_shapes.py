@@ -27,7 +27,12 @@ def skewed_graph(nodes, edges, generator, skew):
     return src, dst
 
 
-@pytest.mark.parametrize("seed", range(28))
+# the 64-channel configuration of the multi-GPU benchmark, which the seeded draw below happens not to pick
+FIXED = {100: ("cfg5", torch.float32, 257, 5000, 1.5), 101: ("cfg5", torch.float32, 1, 40, 0.0),
+         102: ("cfg5", torch.float64, 900, 700, 4.0), 103: ("cfg5", torch.float32, 64, 3, 0.0)}
+
+
+@pytest.mark.parametrize("seed", [*range(28), *FIXED])
 def test_random_shape(seed):
     generator = torch.Generator().manual_seed(1000 + seed)
     pick = lambda n: int(torch.randint(n, (1,), generator=generator))
@@ -38,6 +43,8 @@ def test_random_shape(seed):
     if name in ("cfg2", "cfg4", "wide"):
         edges = min(edges, 700)  # wide rows: keep the oracle quick
     skew = (0.0, 0.0, 1.5, 4.0)[pick(4)]
+    if seed in FIXED:
+        name, dtype, nodes, edges, skew = FIXED[seed]
     in1, in2, out, instructions, options = config(name)
     module = luna.TensorProductConv(in1, in2, out, instructions, internal_weights=False, shared_weights=False,
                                     dtype=dtype, **options)
