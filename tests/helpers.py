@@ -61,8 +61,9 @@ def random_problem(meta_dims, nodes, src, dtype, generator):
 
 
 def tolerance(dtype):
-    """north-star bound: 1e-5 relative in FP32, 1e-12 in FP64, relative to the largest reference magnitude
-    (the reference's rule, tests/testing_utils.py:14-41: max|a - r| <= atol + rtol * max|r|)."""
+    """north-star bound: 1e-5 relative in FP32, 1e-12 in FP64.  "Relative" is checked in both of the reference's
+    senses: the largest deviation over the largest reference magnitude (tests/testing_utils.py:14-41:
+    max|a - r| <= atol + rtol * max|r|) and the relative L2 error |a - r|_2 / |r|_2 (src/utils/testing.py:290-313)."""
     return 1e-5 if dtype == torch.float32 else 1e-12
 
 
@@ -73,6 +74,10 @@ def assert_close(actual, expected, dtype, what=""):
     scale = max(expected.abs().max().item(), 1e-30) if expected.numel() else 1.0
     error = (actual - expected).abs().max().item() if expected.numel() else 0.0
     assert error <= tolerance(dtype) * scale + 1e-300, f"{what}: max error {error:.3e} vs scale {scale:.3e}"
+    norm = expected.norm().item() if expected.numel() else 0.0
+    if norm > 0.0:
+        relative_l2 = (actual - expected).norm().item() / norm
+        assert relative_l2 <= tolerance(dtype), f"{what}: relative L2 error {relative_l2:.3e}"
     return error / scale
 
 
