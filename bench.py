@@ -344,12 +344,24 @@ class ConvWorkload:
         if generic:
             self.op.force_generic(True)
         src, dst, vec = build_graph_edges(name, self.atoms, world, rank, device)
-        self.shard = sharded.make_graph_shard(src, dst, [self.atoms] * world, rank, group=None)
+
+        def timed(fn):  # set-up steps that are not part of the timed step, reported on their own
+            torch.cuda.synchronize()
+            start = time.perf_counter()
+            value = fn()
+            torch.cuda.synchronize()
+            return value, (time.perf_counter() - start) * 1e3
+
+        sharded.make_graph_shard(src, dst, [self.atoms] * world, rank, group=None)  # first use: one-time set-up
+        self.shard, self.graph_build_ms = timed(
+            lambda: sharded.make_graph_shard(src, dst, [self.atoms] * world, rank, group=None))
         self.graph = self.shard.graph
         self.edges = self.graph.num_edges
         self.degrees = [1] if name == "cfg1" else list(range(lmax + 1))
         self.vec = vec.to(dtype)
-        self.sh = luna.spherical_harmonics(self.degrees, self.vec, True, "component").contiguous()
+        luna.spherical_harmonics(self.degrees, self.vec[:1024], True, "component")  # first-use set-up
+        self.sh, self.edge_attr_ms = timed(
+            lambda: luna.spherical_harmonics(self.degrees, self.vec, True, "component").contiguous())
         generator = torch.Generator(device=device).manual_seed(100 + rank)
         op = self.op
         self.x = torch.randn(self.atoms, op.in1_dim, device=device, dtype=dtype, generator=generator)
@@ -409,7 +421,9 @@ class ConvWorkload:
         result = {"edges_rank0": self.edges, "edges_total": int(edges_total.item()),
                   "source_rows_rank0": self.graph.source_rows, "halo_rows_rank0": self.shard.halo_rows,
                   "kernels": "staged" if op.uses_staged_kernels else "table-driven",
-                  "backward_variant": op.backward_variant}
+                  "backward_variant": op.backward_variant,
+                  # outside the timed step (built once per topology / per geometry), wall clock with a synchronise
+                  "graph_build_ms": self.graph_build_ms, "edge_attr_harmonics_ms": self.edge_attr_ms}
         if self.name == "cfg3":
             ms, _ = time_steps(self.force_step, steps, warmup, 2, self.world, sampler)
             # minimum traffic of the step: three reads of the weights (forward, backward for gy, tangent forward)
@@ -738,7 +752,8 @@ def main():
             "dtype": "f64" if dtype == torch.float64 else "f32", "data": "synthetic",
             "config": static_config(name, args.atoms_per_gpu, world),
             "graph": {k: result[k] for k in ("edges_rank0", "edges_total", "source_rows_rank0", "halo_rows_rank0",
-                                             "kernels", "backward_variant")},
+                                             "kernels", "backward_variant", "graph_build_ms",
+                                             "edge_attr_harmonics_ms")},
             "roofline": dict(result["roofline"], secondary=secondary_roofline(name, result, peaks)),
             "fma_peaks": peaks, "collective_ms": result.get("collective_ms"), "parity": parity,
             "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "others": others,
